@@ -402,6 +402,108 @@ FMS_API int fms_normed_add_rmsnorm(float* residual, const void* delta, int has_p
 }
 
 // ---------------------------------------------------------------------------------------------------
+// The same step for norms of either kind, each chosen by a mode: 0 none, 1 root mean square, 2 layer norm (the mean is
+// taken off first and the variance is the mean of the squared deviations; no bias).  Gains are float32 vectors of
+// `dim` (a layer scale that multiplies a norm's result is folded into its gain by the caller):
+//   d = post(delta) * post_gain                              post_mode 0: d = delta
+//   x = residual[src] + d                float32; written back to residual unless rows are gathered
+//   out[r] = norm(x) * gain                                   out_mode 0: out[r] = x, the stream in the compute dtype
+//                                                             (no out pointer: nothing but the sum is wanted)
+// A block per row with the row in registers, NPER values a thread (dim <= NPER * blockDim).
+// ---------------------------------------------------------------------------------------------------
+template <int NPER>
+__device__ __forceinline__ void norm_in_registers(float (&v)[NPER], int mode, const float* gain_vec, float eps, int dim,
+                                                  float* scratch) {
+  if (mode == 0) return;
+  float mean = 0.f;
+  if (mode == 2) {
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < NPER; ++j) sum += v[j];  // values beyond the row are zeros
+    mean = block_sum(sum, scratch) / (float)dim;
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < NPER; ++j) {
+    const int d = threadIdx.x + j * blockDim.x;
+    const float c = d < dim ? v[j] - mean : 0.f;
+    v[j] = c;
+    ss += c * c;
+  }
+  const float inv = 1.f / sqrtf(block_sum(ss, scratch) / (float)dim + eps);
+#pragma unroll
+  for (int j = 0; j < NPER; ++j) {
+    const int d = threadIdx.x + j * blockDim.x;
+    if (d < dim) v[j] = v[j] * inv * gain_vec[d];
+  }
+}
+
+template <typename T, int NPER>
+__global__ void normed_add_norm_kernel(float* residual, const T* delta, int post_mode, const float* post_gain, float post_eps,
+                                       int out_mode, const float* gain, float eps, T* out, const int* rows, int dim,
+                                       int residual_rows) {
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  if (!FMS_IN(src, residual_rows)) return;  // the whole block alike
+  float* res = residual + (size_t)src * dim;
+  float x[NPER];
+  if (delta) {
+    const T* del = delta + (size_t)src * dim;
+    float v[NPER];
+#pragma unroll
+    for (int j = 0; j < NPER; ++j) {
+      const int d = threadIdx.x + j * blockDim.x;
+      v[j] = d < dim ? to_f32(del[d]) : 0.f;
+    }
+    norm_in_registers<NPER>(v, post_mode, post_gain, post_eps, dim, scratch);
+#pragma unroll
+    for (int j = 0; j < NPER; ++j) {
+      const int d = threadIdx.x + j * blockDim.x;
+      x[j] = d < dim ? res[d] + v[j] : 0.f;
+      if (d < dim && rows == nullptr) res[d] = x[j];
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < NPER; ++j) {
+      const int d = threadIdx.x + j * blockDim.x;
+      x[j] = d < dim ? res[d] : 0.f;
+    }
+  }
+  if (out == nullptr) return;
+  norm_in_registers<NPER>(x, out_mode, gain, eps, dim, scratch);
+  T* o = out + (size_t)r * dim;
+#pragma unroll
+  for (int j = 0; j < NPER; ++j) {
+    const int d = threadIdx.x + j * blockDim.x;
+    if (d < dim) o[d] = from_f32<T>(x[j]);
+  }
+}
+
+FMS_API int fms_normed_add_norm(float* residual, const void* delta, int post_mode, const float* post_gain, float post_eps,
+                                int out_mode, const float* gain, float eps, void* out, int dtype, const int* rows,
+                                int n_rows, int dim, int residual_rows, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (dim <= 0 || dim > 16384) return fms_fail("normed_add_norm: rows of %d values (up to 16384)", dim);
+  if (post_mode < 0 || post_mode > 2 || out_mode < 0 || out_mode > 2) return fms_fail("normed_add_norm: modes %d, %d", post_mode, out_mode);
+  if ((post_mode && delta && !post_gain) || (out_mode && out && !gain)) return fms_fail("normed_add_norm: a norm without its gain");
+  const int threads = dim >= 4096 ? 1024 : (dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128));
+  const int nper = (dim + threads - 1) / threads;
+#define FMS_NAN(NPER)                                                                                                     \
+  FMS_DISPATCH_DTYPE(dtype, T, fms_launch(normed_add_norm_kernel<T, NPER>, dim3(n_rows), dim3(threads), 0, stream, residual,   \
+                                          (const T*)delta, post_mode, post_gain, post_eps, out_mode, gain, eps, (T*)out, rows, \
+                                          dim, residual_rows))
+  if (nper <= 2) FMS_NAN(2);
+  else if (nper <= 4) FMS_NAN(4);
+  else if (nper <= 8) FMS_NAN(8);
+  else FMS_NAN(16);
+#undef FMS_NAN
+  return fms_launch_status("normed_add_norm");
+}
+
+// ---------------------------------------------------------------------------------------------------
 // gated activation: out[n, f] = act(gu[n, f]) * gu[n, hidden + f]   (fms/modules/feedforward.py:291-292)
 // ---------------------------------------------------------------------------------------------------
 __device__ __forceinline__ float activate(float g, int act) {
@@ -778,7 +880,10 @@ FMS_API int fms_cast_rows(const float* x, void* out, int dtype, long n, cudaStre
 // the key size:
 //   proj[t] = [q: nheads x dim | k: kvheads x dim | v: kvheads x vdim | ...]   (row stride `stride`)
 //   q, k: pairs (2i, 2i+1), i < rot / 2, rotated by position * inv_freq[i]; the other values pass
+//         (`halves`: the pairs are (i, i + rot / 2) instead)
 //   q, k: x / sqrt(mean(x^2) + eps) over the head's dim values, where qk_norm is set (no gain)
+//         (`norm_first`: the norm comes before the rotation, times q_gain / k_gain [dim] where those are given)
+//   `v_from_k`: there are no value columns; the value is the key as projected, before norm and rotation
 //   q -> q_out[t, head, 0..pad) ; k, v -> the cache row of the token's slot and place, each `pad` wide:
 //   values beyond dim (vdim) are zeros, so that kernels built for one head size `pad` serve both
 // A warp per (token, head), four a block; float32 arithmetic.
@@ -787,7 +892,8 @@ constexpr int PREP_MAX_PAIRS = 256;
 
 template <typename T>
 __global__ void qk_prepare_store_kernel(const T* proj, int stride, T* q_out, const float* inv_freq, int rot,
-                                        int qk_norm, float eps, const int* positions, const int* position_ids,
+                                        int qk_norm, float eps, const float* q_gain, const float* k_gain, int norm_first,
+                                        int halves, int v_from_k, const int* positions, const int* position_ids,
                                         const int* token_seq, const int* slots, T* k_cache, T* v_cache, const int* table,
                                         int table_stride, int block_tokens, int nheads, int kvheads, int dim, int vdim,
                                         int pad, int write_cache, int* error_flag, int n_seqs, int table_rows,
@@ -829,7 +935,7 @@ __global__ void qk_prepare_store_kernel(const T* proj, int stride, T* q_out, con
     if (item >= nheads + kvheads) {  // a value head: copied and padded
       const int h = item - nheads - kvheads;
       if (vrow == nullptr) return;
-      const T* src = row + (size_t)(nheads + kvheads) * dim + (size_t)h * vdim;
+      const T* src = v_from_k ? row + (size_t)(nheads + h) * dim : row + (size_t)(nheads + kvheads) * dim + (size_t)h * vdim;
       T* dst = vrow + (size_t)h * block_tokens * pad;
       for (int e = lane; e < pad; e += 32) dst[e] = e < vdim ? src[e] : from_f32<T>(0.f);
       return;
@@ -839,9 +945,30 @@ __global__ void qk_prepare_store_kernel(const T* proj, int stride, T* q_out, con
     T* dst = is_q ? q_out + ((size_t)t * nheads + item) * pad
                   : (krow ? krow + (size_t)(item - nheads) * block_tokens * pad : nullptr);
     if (dst == nullptr) return;
+    const int half = rot / 2;
+    if (norm_first) {
+      // the norm (with its gain, where there is one) comes first and the rotation turns the normed values
+      const float* gain = is_q ? q_gain : k_gain;
+      float ss = 0.f;
+      for (int e = lane; e < dim; e += 32) {
+        const float x = to_f32(src[e]);
+        ss += x * x;
+      }
+      const float inv = qk_norm ? 1.f / sqrtf(warp_sum(ss) / (float)dim + eps) : 1.f;
+      for (int i = lane; i < half; i += 32) {
+        const int a = halves ? i : 2 * i, b = halves ? i + half : 2 * i + 1;
+        const float x0 = to_f32(src[a]) * inv * (gain ? gain[a] : 1.f), x1 = to_f32(src[b]) * inv * (gain ? gain[b] : 1.f);
+        dst[a] = from_f32<T>(sc[i].y * x0 - sc[i].x * x1);
+        dst[b] = from_f32<T>(sc[i].y * x1 + sc[i].x * x0);
+      }
+      for (int e = rot + lane; e < pad; e += 32)
+        dst[e] = from_f32<T>(e < dim ? to_f32(src[e]) * inv * (gain ? gain[e] : 1.f) : 0.f);
+      return;
+    }
     float ss = 0.f;
-    for (int i = lane; i < rot / 2; i += 32) {
-      const float x0 = to_f32(src[2 * i]), x1 = to_f32(src[2 * i + 1]);
+    for (int i = lane; i < half; i += 32) {
+      const int a = halves ? i : 2 * i, b = halves ? i + half : 2 * i + 1;
+      const float x0 = to_f32(src[a]), x1 = to_f32(src[b]);
       const float r0 = sc[i].y * x0 - sc[i].x * x1, r1 = sc[i].y * x1 + sc[i].x * x0;
       ss += r0 * r0 + r1 * r1;
     }
@@ -850,17 +977,19 @@ __global__ void qk_prepare_store_kernel(const T* proj, int stride, T* q_out, con
       ss += x * x;
     }
     const float inv = qk_norm ? 1.f / sqrtf(warp_sum(ss) / (float)dim + eps) : 1.f;
-    for (int i = lane; i < rot / 2; i += 32) {
-      const float x0 = to_f32(src[2 * i]), x1 = to_f32(src[2 * i + 1]);
-      dst[2 * i] = from_f32<T>((sc[i].y * x0 - sc[i].x * x1) * inv);
-      dst[2 * i + 1] = from_f32<T>((sc[i].y * x1 + sc[i].x * x0) * inv);
+    for (int i = lane; i < half; i += 32) {
+      const int a = halves ? i : 2 * i, b = halves ? i + half : 2 * i + 1;
+      const float x0 = to_f32(src[a]), x1 = to_f32(src[b]);
+      dst[a] = from_f32<T>((sc[i].y * x0 - sc[i].x * x1) * inv);
+      dst[b] = from_f32<T>((sc[i].y * x1 + sc[i].x * x0) * inv);
     }
     for (int e = rot + lane; e < pad; e += 32) dst[e] = from_f32<T>(e < dim ? to_f32(src[e]) * inv : 0.f);
   }
 }
 
 FMS_API int fms_qk_prepare_store(const void* proj, int dtype, int stride, void* q_out, const float* inv_freq, int rot,
-                                 int qk_norm, float eps, const int* positions, const int* position_ids,
+                                 int qk_norm, float eps, const float* q_gain, const float* k_gain, int norm_first,
+                                 int halves, int v_from_k, const int* positions, const int* position_ids,
                                  const int* token_seq, const int* slots, void* k_cache, void* v_cache, const int* table,
                                  int table_stride, int block_tokens, int n_tokens, int nheads, int kvheads, int dim,
                                  int vdim, int pad, int write_cache, int* error_flag, int n_seqs, int table_rows,
@@ -869,10 +998,13 @@ FMS_API int fms_qk_prepare_store(const void* proj, int dtype, int stride, void* 
   if (rot < 0 || rot % 2 || rot > dim || rot / 2 > PREP_MAX_PAIRS || (rot > 0 && inv_freq == nullptr))
     return fms_fail("qk_prepare_store: %d rotated values of %d", rot, dim);
   if (dim <= 0 || vdim <= 0 || pad < dim || pad < vdim) return fms_fail("qk_prepare_store: dim %d, vdim %d, pad %d", dim, vdim, pad);
+  if (v_from_k && vdim != dim) return fms_fail("qk_prepare_store: values that are the keys have the keys' size, not %d for %d", vdim, dim);
+  if ((q_gain || k_gain) && !norm_first) return fms_fail("qk_prepare_store: gains belong to the norm that comes before the rotation");
   FMS_DISPATCH_DTYPE(dtype, T,
                      fms_launch(qk_prepare_store_kernel<T>, dim3(n_tokens, (nheads + 2 * kvheads + 3) / 4), dim3(128), 0, stream,
                                 (const T*)proj, stride,
-                                (T*)q_out, inv_freq, rot, qk_norm, eps, positions, position_ids, token_seq, slots,
+                                (T*)q_out, inv_freq, rot, qk_norm, eps, q_gain, k_gain, norm_first, halves, v_from_k,
+                                positions, position_ids, token_seq, slots,
                                 (T*)k_cache, (T*)v_cache, table, table_stride, block_tokens, nheads, kvheads, dim, vdim, pad,
                                 write_cache, error_flag, n_seqs, table_rows, pool_blocks));
   return fms_launch_status("qk_prepare_store");
@@ -881,11 +1013,12 @@ FMS_API int fms_qk_prepare_store(const void* proj, int dtype, int stride, void* 
 // ---------------------------------------------------------------------------------------------------
 // gate on the heads' results: out[t, h * vdim + e] = factor * o[t, h * pad + e] * sigmoid(gate[t, h * vdim + e]),
 // e < vdim; o has rows of nheads * pad, gate is a run of columns of a wider matrix (row stride gate_stride)
+// `per_head`: one gate a head, sigmoid(gate[t, h]), instead of one a value
 // ---------------------------------------------------------------------------------------------------
 // VEC values a thread (4 where the sizes and addresses allow accesses of 4 values, else 1)
 template <typename T, int VEC>
 __global__ void sigmoid_gate_kernel(const T* o, const T* gate, int gate_stride, T* out, int nheads, int vdim, int pad,
-                                    float factor, size_t total) {
+                                    float factor, int per_head, size_t total) {
   pdl_launch_dependents();
   pdl_wait();
   const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC;
@@ -896,31 +1029,32 @@ __global__ void sigmoid_gate_kernel(const T* o, const T* gate, int gate_stride, 
   if constexpr (VEC == 4) {
     float v[4], g[4];
     ldv4(o + (t * nheads + h) * pad + e, v);
-    if (gate) ldv4(gate + t * gate_stride + c, g);
+    if (gate && per_head) g[0] = g[1] = g[2] = g[3] = to_f32(gate[t * gate_stride + h]);
+    else if (gate) ldv4(gate + t * gate_stride + c, g);
 #pragma unroll
     for (int k = 0; k < 4; ++k) v[k] = v[k] * factor * (gate ? 1.f / (1.f + expf(-g[k])) : 1.f);
     stv4(out + i, v);
   } else {
     float v = to_f32(o[(t * nheads + h) * pad + e]) * factor;
-    if (gate) v *= 1.f / (1.f + expf(-to_f32(gate[t * gate_stride + c])));
+    if (gate) v *= 1.f / (1.f + expf(-to_f32(gate[t * gate_stride + (per_head ? h : c)])));
     out[i] = from_f32<T>(v);
   }
 }
 
 FMS_API int fms_sigmoid_gate(const void* o, const void* gate, int gate_stride, void* out, int dtype, int n_tokens,
-                             int nheads, int vdim, int pad, float factor, cudaStream_t stream) {
+                             int nheads, int vdim, int pad, float factor, int per_head, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   const size_t total = (size_t)n_tokens * nheads * vdim;
   const size_t item = dtype == FMS_BF16 ? 2 : 4;
   const bool four = vdim % 4 == 0 && pad % 4 == 0 && (uintptr_t)o % (4 * item) == 0 && (uintptr_t)out % (4 * item) == 0 &&
-                    (gate == nullptr || (gate_stride % 4 == 0 && (uintptr_t)gate % (4 * item) == 0));
+                    (gate == nullptr || per_head || (gate_stride % 4 == 0 && (uintptr_t)gate % (4 * item) == 0));
   if (four) {
     FMS_DISPATCH_DTYPE(dtype, T, fms_launch(sigmoid_gate_kernel<T, 4>, dim3((unsigned)((total / 4 + 255) / 256)), dim3(256), 0,
                                             stream, (const T*)o, (const T*)gate, gate_stride, (T*)out, nheads, vdim, pad,
-                                            factor, total));
+                                            factor, per_head, total));
   } else {
     FMS_DISPATCH_DTYPE(dtype, T, fms_launch(sigmoid_gate_kernel<T, 1>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream,
-                                            (const T*)o, (const T*)gate, gate_stride, (T*)out, nheads, vdim, pad, factor, total));
+                                            (const T*)o, (const T*)gate, gate_stride, (T*)out, nheads, vdim, pad, factor, per_head, total));
   }
   return fms_launch_status("sigmoid_gate");
 }

@@ -11,6 +11,11 @@
 //   delta_rule_scan     per head, S [dim, vdim]:  S = diag(g) S;  u = beta (v - S^T k);  S = S + k u^T;  o = S^T q
 //                       with q, k unit vectors (q also times dim^-1/2), beta = sigmoid(b), g = exp(-exp(A_log) softplus(a + dt_bias)),
 //                       all of which delta_prepare makes ready for every token before the scan starts
+//   decay_scan          per head, S [dim, vdim]:  S = a S + b k v^T;  o = S^T q, with one decay a a head and b = 1, or with
+//                       a and b from exponential gates under a running maximum m (m' = max(f + m, i), a = exp(f + m - m'),
+//                       b = exp(i - m')), a normalizer n = a n + b k and o = S^T q / (max(|n.q|, exp(-m')) + 1e-6);
+//                       linear_prepare makes q, k, v float32 (an activation, a factor on q), exp_gates walks the maxima
+//                       and the normalizer and leaves (a, b, 1 / denominator) for every token
 //   gated_group_rmsnorm rows cut into groups, each divided by its own root mean square, times a weight; a gate
 //                       multiplies either before the norm (silu) or after it (sigmoid)
 //
@@ -505,6 +510,206 @@ __global__ void __launch_bounds__(SCAN_THREADS) delta_rule_scan_kernel(const flo
   }
 }
 
+// ---- state matrices under scalar decays ---------------------------------------------------------------
+// The first `cols` columns of the projection's rows, in float32: act 1 takes silu, and the first `q_cols` columns are
+// multiplied by q_scale.  VEC values a thread.
+template <typename T, int VEC>
+__global__ void linear_prepare_kernel(const T* proj, int stride, float* out, int cols, int q_cols, float q_scale, int act,
+                                      size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC;
+  if (i >= total) return;
+  const size_t t = i / cols;
+  const int c = (int)(i - t * cols);
+  float v[VEC];
+  load_channels<VEC>(proj + t * stride + c, v);
+#pragma unroll
+  for (int k = 0; k < VEC; ++k) {
+    if (act == 1) v[k] = v[k] * sigmoid_f(v[k]);
+    if (c + k < q_cols) v[k] *= q_scale;
+  }
+  if constexpr (VEC == 4) *reinterpret_cast<float4*>(out + i) = make_float4(v[0], v[1], v[2], v[3]);
+  else out[i] = v[0];
+}
+
+// Exponential gates under a running maximum with their normalizer, a warp per (sequence, head).  gate_raw: column h
+// of the rows is head h's input gate before its bias, column heads + h its forget gate; bias [2 heads] float32; cap > 0:
+//   i = cap tanh((raw_i + bias_i) / cap);  f = logsigmoid(cap tanh((raw_f + bias_f) / cap))
+//   m' = max(f + m, i);  a = exp(f + m - m');  b = exp(i - m');  n' = a n + b k
+//   gates[t, h] = (a, b, 1 / (max(|n'.q|, exp(-m')) + 1e-6))
+// norm_state holds per slot and head the normalizer n (dim values) and then m, zeros for a new sequence; both are left
+// at their values after the step's last row.  q and k are read from qkv (float32 rows q | k | v, head by head).  The
+// lanes take a token each for the gates and exponentials; maxima and normalizer are walked in order by the whole warp,
+// a lane holding every 32nd value of n.  No other kernel touches norm_state, so nothing of it is read while it changes.
+constexpr int GATE_RUNS = 8;  // dim <= 32 * GATE_RUNS
+
+template <typename T>
+__global__ void exp_gates_kernel(const T* gate_raw, int stride, const float* bias, float cap, const float* qkv, int row_w,
+                                 float* norm_state, float* gates, const int* first_row, const int* slots, int heads,
+                                 int dim, int write_state, int n_seqs, int n_slots) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (unit >= n_seqs * heads) return;
+  const int seq = unit / heads, head = unit - seq * heads;
+  const int slot = __ldcg(slots + seq);
+  if (!FMS_IN(slot, n_slots)) return;
+  const int lo = first_row[seq], hi = first_row[seq + 1];
+  float* st = norm_state + ((size_t)slot * heads + head) * (dim + 1);
+  float m = st[dim];
+  float n[GATE_RUNS];
+#pragma unroll
+  for (int r = 0; r < GATE_RUNS; ++r) n[r] = (r * 32 + lane < dim) ? st[r * 32 + lane] : 0.f;
+  const float bi = bias[head], bf = bias[heads + head];
+  const float* qh = qkv + (size_t)head * dim;
+  const float* kh = qkv + (size_t)(heads + head) * dim;
+  for (int base = lo; base < hi; base += 32) {
+    const int t = base + lane;
+    float gi = 0.f, gf = 0.f;
+    if (t < hi) {
+      gi = cap * tanhf((to_f32(gate_raw[(size_t)t * stride + head]) + bi) / cap);
+      const float z = cap * tanhf((to_f32(gate_raw[(size_t)t * stride + heads + head]) + bf) / cap);
+      gf = z < 0.f ? z - log1pf(expf(z)) : -log1pf(expf(-z));
+    }
+    float before = 0.f, after = 0.f;
+    const int cn = min(32, hi - base);
+    for (int j = 0; j < cn; ++j) {
+      const float ij = __shfl_sync(0xffffffffu, gi, j), fj = __shfl_sync(0xffffffffu, gf, j);
+      const float next = fmaxf(fj + m, ij);
+      if (lane == j) {
+        before = m;
+        after = next;
+      }
+      m = next;
+    }
+    const float keep = expf(gf + before - after), take = expf(gi - after);
+    float nq = 0.f;
+#pragma unroll 4
+    for (int j = 0; j < cn; ++j) {
+      const float aj = __shfl_sync(0xffffffffu, keep, j), bj = __shfl_sync(0xffffffffu, take, j);
+      const size_t at = (size_t)(base + j) * row_w;
+      float part = 0.f;
+#pragma unroll
+      for (int r = 0; r < GATE_RUNS; ++r) {
+        if (r * 32 < dim) {
+          const int e = r * 32 + lane;
+          const float kk = e < dim ? kh[at + e] : 0.f, qq = e < dim ? qh[at + e] : 0.f;
+          n[r] = fmaf(aj, n[r], bj * kk);
+          part = fmaf(n[r], qq, part);
+        }
+      }
+      part = warp_sum(part);
+      if (lane == j) nq = part;
+    }
+    if (t < hi) {
+      float* g = gates + ((size_t)t * heads + head) * 3;
+      g[0] = keep;
+      g[1] = take;
+      g[2] = 1.f / (fmaxf(fabsf(nq), expf(-after)) + 1e-6f);
+    }
+  }
+  if (write_state) {
+#pragma unroll
+    for (int r = 0; r < GATE_RUNS; ++r)
+      if (r * 32 + lane < dim) st[r * 32 + lane] = n[r];
+    if (lane == 0) st[dim] = m;
+  }
+}
+
+// qkv [tokens, 2 heads * dim + heads * vdim] float32: q | k | v, head by head; o [tokens, heads * vdim].
+// GATED: per token and head (a, b, c) in gates [tokens, heads, 3]: S = a S + b k v^T, o = c S^T q; else one decay a head
+// (decay [heads]): S = decay S + k v^T, o = S^T q.
+template <int NP, int VP, int PARTS, bool GATED>
+__global__ void __launch_bounds__(SCAN_THREADS) decay_scan_kernel(const float* qkv, const float* gates, const float* decay,
+                                                                  float* state, float* o, const int* first_row,
+                                                                  const int* slots, int heads, int dim, int vdim,
+                                                                  int write_state, int n_slots, int vec_qk, int vec_v) {
+  constexpr int GROUPS = SCAN_THREADS / PARTS, NPAD = RowLayout<NP, PARTS>::ROW, RUN = RowLayout<NP, PARTS>::RUN, VB = GROUPS * VP;
+  extern __shared__ __align__(16) float smem[];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int seq = blockIdx.x, head = blockIdx.y, v0 = blockIdx.z * VB;
+  const int tid = threadIdx.x, part = tid % PARTS, grp = tid / PARTS;
+  const int slot = __ldcg(slots + seq);
+  if (!FMS_IN(slot, n_slots)) return;
+  const int lo = first_row[seq], hi = first_row[seq + 1];
+  const int row_w = 2 * heads * dim + heads * vdim;
+  constexpr int STAGE = CH * (2 * NPAD + VB + 4);
+  const int cols = min(VB, vdim - v0);
+  if (dim != PARTS * NP || cols != VB)
+    for (int i = tid; i < 2 * STAGE; i += blockDim.x) smem[i] = 0.f;  // the padding stays zero from here on
+  float s[VP][NP];
+#pragma unroll
+  for (int i = 0; i < VP; ++i) {
+    const int v = v0 + grp * VP + i;
+    load_state<NP, PARTS>(state + (((size_t)slot * heads + head) * vdim + (v < vdim ? v : 0)) * dim, part, dim, v < vdim, s[i]);
+  }
+  const float fixed = GATED ? 1.f : decay[head];
+  __syncthreads();
+  auto issue = [&](int c0, int stage) {
+    const int cn = min(CH, hi - c0);
+    float* base = smem + stage * STAGE;
+    const float* src = qkv + (size_t)c0 * row_w;
+    stage_runs<NP, PARTS>(base, src + (size_t)head * dim, row_w, cn, dim, vec_qk);
+    stage_runs<NP, PARTS>(base + CH * NPAD, src + (size_t)(heads + head) * dim, row_w, cn, dim, vec_qk);
+    stage_rows(base + 2 * CH * NPAD, VB, src + 2 * (size_t)heads * dim + (size_t)head * vdim + v0, row_w, cn, cols, vec_v);
+    if (GATED) stage_rows(base + 2 * CH * NPAD + CH * VB, 4, gates + ((size_t)c0 * heads + head) * 3, (size_t)heads * 3, cn, 3, false);
+    cp_async_commit();
+  };
+  if (lo < hi) issue(lo, 0);
+  int stage = 0;
+  for (int c0 = lo; c0 < hi; c0 += CH, stage ^= 1) {
+    const int cn = min(CH, hi - c0);
+    const bool more = c0 + CH < hi;
+    if (more) issue(c0 + CH, stage ^ 1);
+    if (more) cp_async_wait<1>(); else cp_async_wait<0>();
+    __syncthreads();
+    const float* sq = smem + stage * STAGE;
+    const float* sk = sq + CH * NPAD;
+    const float* sv = sk + CH * NPAD;
+    const float* sg = sv + CH * VB;
+    for (int t = 0; t < cn; ++t) {
+      float q[NP], k[NP];
+      load_run<NP>(sk + t * NPAD + part * RUN, k);
+      load_run<NP>(sq + t * NPAD + part * RUN, q);
+      const float a = GATED ? sg[t * 4] : fixed;
+      float acc[VP], val[VP];
+#pragma unroll
+      for (int i = 0; i < VP; ++i) {
+        acc[i] = 0.f;
+        val[i] = sv[t * VB + grp * VP + i] * (GATED ? sg[t * 4 + 1] : 1.f);
+      }
+#pragma unroll
+      for (int j = 0; j < NP; ++j) {
+        const float kj = k[j], qj = q[j];
+#pragma unroll
+        for (int i = 0; i < VP; ++i) {
+          s[i][j] = fmaf(a, s[i][j], kj * val[i]);
+          acc[i] = fmaf(s[i][j], qj, acc[i]);
+        }
+      }
+      const float scale = GATED ? sg[t * 4 + 2] : 1.f;
+#pragma unroll
+      for (int i = 0; i < VP; ++i) {
+        acc[i] = group_sum<PARTS>(acc[i]);
+        const int v = v0 + grp * VP + i;
+        if (part == i && v < vdim) o[(size_t)(c0 + t) * heads * vdim + (size_t)head * vdim + v] = acc[i] * scale;
+      }
+    }
+    __syncthreads();  // this stage is free again
+  }
+  if (write_state) {
+#pragma unroll
+    for (int i = 0; i < VP; ++i) {
+      const int v = v0 + grp * VP + i;
+      if (v >= vdim) continue;
+      store_state<NP, PARTS>(state + (((size_t)slot * heads + head) * vdim + v) * dim, part, dim, s[i]);
+    }
+  }
+}
+
 // ---- norm over groups of a row, with a gate ----------------------------------------------------------
 // x [tokens, width] float32; groups of `gs` values; weight[c % weight_period]; gate: columns of rows of gate_stride
 // values.  gate_mode 1: x * silu(gate) before the norm;  2: sigmoid(gate) after the norm and the weight;  0: none.
@@ -736,6 +941,65 @@ FMS_API int fms_delta_rule_scan(float* qkv, const void* beta_raw, int dtype, int
   FMS_SCAN_SHAPES(FMS_LAUNCH);
 #undef FMS_LAUNCH
   return fms_launch_status("delta_rule_scan");
+}
+
+// q | k | v of a step's rows in float32 from the first columns of the projection's rows (bfloat16 or float32):
+// act 1 takes silu of every value; the first q_cols columns are multiplied by q_scale
+FMS_API int fms_linear_prepare(const void* proj, int dtype, int stride, float* out, int n_tokens, int cols, int q_cols,
+                               float q_scale, int act, cudaStream_t stream) {
+  if (n_tokens <= 0 || cols <= 0) return 0;
+  const size_t total = (size_t)n_tokens * cols;
+  const size_t item = dtype == FMS_BF16 ? 2 : 4;
+  const bool four = cols % 4 == 0 && stride % 4 == 0 && (uintptr_t)proj % (4 * item) == 0 && (uintptr_t)out % 16 == 0;
+  if (four) {
+    FMS_DISPATCH_DTYPE(dtype, T, fms_launch(linear_prepare_kernel<T, 4>, dim3((unsigned)((total / 4 + 255) / 256)), dim3(256), 0,
+                                            stream, (const T*)proj, stride, out, cols, q_cols, q_scale, act, total));
+  } else {
+    FMS_DISPATCH_DTYPE(dtype, T, fms_launch(linear_prepare_kernel<T, 1>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0,
+                                            stream, (const T*)proj, stride, out, cols, q_cols, q_scale, act, total));
+  }
+  return fms_launch_status("linear_prepare");
+}
+
+// qkv [tokens, 2 heads * dim + heads * vdim] float32.  With gate_raw (columns [i: heads | f: heads] of rows of
+// gate_stride values, bias [2 heads], cap): exponential gates, with normalizer and running maximum in norm_state
+// [slots, heads, dim + 1]; gates [tokens, heads, 3] is float32 scratch of the caller's.  Without: decay [heads].
+FMS_API int fms_decay_scan(const float* qkv, const void* gate_raw, int dtype, int gate_stride, const float* gate_bias,
+                           float cap, float* gates, const float* decay, float* state, float* norm_state, float* o,
+                           const int* first_row, const int* slots, int n_tokens, int n_seqs, int heads, int dim, int vdim,
+                           int write_state, int n_slots, cudaStream_t stream) {
+  if (n_seqs <= 0 || n_tokens <= 0) return 0;
+  if (heads <= 0 || dim <= 0 || dim > 256 || vdim <= 0)
+    return fms_fail("decay_scan: %d heads, dim %d (up to 256), vdim %d", heads, dim, vdim);
+  const bool gated = gate_raw != nullptr;
+  if (gated && (!gate_bias || !gates || !norm_state || !(cap > 0.f))) return fms_fail("decay_scan: gates without bias, scratch, normalizer or cap");
+  if (!gated && !decay) return fms_fail("decay_scan: neither gates nor decays");
+  const long row_w = 2L * heads * dim + (long)heads * vdim;
+  if (gated) {
+    FMS_DISPATCH_DTYPE(dtype, T, fms_launch(exp_gates_kernel<T>, dim3((n_seqs * heads + 3) / 4), dim3(128), 0, stream,
+                                            (const T*)gate_raw, gate_stride, gate_bias, cap, qkv, (int)row_w, norm_state, gates,
+                                            first_row, slots, heads, dim, write_state, n_seqs, n_slots));
+  }
+  const ScanShape shape = scan_shape(n_seqs, heads, vdim, dim);
+  const int vb = SCAN_THREADS / shape.parts * shape.vp;  // value columns of a block
+  const int vec_qk = rows_allow_16(qkv, 0, row_w, dim) && shape.np % 4 == 0;
+  const int vec_v = rows_allow_16(qkv, 2L * heads * dim, row_w, vdim) && vdim % vb == 0 && vb % 4 == 0;
+  const dim3 grid(n_seqs, heads, (vdim + vb - 1) / vb), block(SCAN_THREADS);
+#define FMS_LAUNCH_G(NP, VP, PARTS, GATED)                                                                              \
+  do {                                                                                                                  \
+    const size_t smem = ((size_t)2 * CH * (2 * RowLayout<NP, PARTS>::ROW + SCAN_THREADS / PARTS * VP + 4)) * sizeof(float); \
+    cudaFuncSetAttribute(decay_scan_kernel<NP, VP, PARTS, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    fms_launch(decay_scan_kernel<NP, VP, PARTS, GATED>, grid, block, smem, stream, qkv, (const float*)gates, decay, state, \
+               o, first_row, slots, heads, dim, vdim, write_state, n_slots, vec_qk, vec_v);                               \
+  } while (0)
+#define FMS_LAUNCH_T(NP, VP, PARTS) FMS_LAUNCH_G(NP, VP, PARTS, true)
+#define FMS_LAUNCH_F(NP, VP, PARTS) FMS_LAUNCH_G(NP, VP, PARTS, false)
+  if (gated) FMS_SCAN_SHAPES(FMS_LAUNCH_T);
+  else FMS_SCAN_SHAPES(FMS_LAUNCH_F);
+#undef FMS_LAUNCH_T
+#undef FMS_LAUNCH_F
+#undef FMS_LAUNCH_G
+  return fms_launch_status("decay_scan");
 }
 
 FMS_API int fms_gated_group_rmsnorm(const float* x, const void* gate, int dtype, int gate_stride, int gate_mode,

@@ -67,9 +67,12 @@ _SIGNATURES = {
                              _I, _I, _P],
     "fms_scaled_add_rmsnorm": [_P, _F, _P, _F, _P, _F, _P, _I, _F, _P, _I, _I, _I, _P],
     "fms_cast_rows": [_P, _P, _I, _L, _P],
-    "fms_qk_prepare_store": [_P, _I, _I, _P, _P, _I, _I, _F, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I,
-                             _P, _I, _I, _I, _P],
-    "fms_sigmoid_gate": [_P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _P],
+    "fms_qk_prepare_store": [_P, _I, _I, _P, _P, _I, _I, _F, _P, _P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I,
+                             _I, _I, _I, _I, _I, _P, _I, _I, _I, _P],
+    "fms_sigmoid_gate": [_P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _P],
+    "fms_normed_add_norm": [_P, _P, _I, _P, _F, _I, _P, _F, _P, _I, _P, _I, _I, _I, _P],
+    "fms_linear_prepare": [_P, _I, _I, _P, _I, _I, _I, _F, _I, _P],
+    "fms_decay_scan": [_P, _P, _I, _I, _P, _F, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "fms_attention_prefill_sink": [_P, _P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P, _P,
                                    _P],
     "fms_attention_decode_sink": [_P, _P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _F, _I, _I, _I, _L,
@@ -241,6 +244,33 @@ def normed_add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], po
           float(post_num), float(post_eps), _ptr(gain_vec), float(gain_num), float(eps),
           _code(vecs[0].dtype) if vecs else F32, _ptr(out), _code(out_dtype), _ptr(rows), n, dim, residual.shape[0],
           _stream())
+    return out
+
+
+NORM_NONE, NORM_RMS, NORM_LAYER = 0, 1, 2
+
+
+def normed_add_norm(residual: torch.Tensor, delta: Optional[torch.Tensor], post, out_norm, out_dtype: torch.dtype,
+                    rows: Optional[torch.Tensor] = None, want_out: bool = True) -> Optional[torch.Tensor]:
+    """residual (float32, in place) += post(delta); returns out_norm(residual) in ``out_dtype``.  ``post`` and
+    ``out_norm`` are (mode, gain, eps) with mode ``NORM_NONE`` (the rows as they are), ``NORM_RMS`` or ``NORM_LAYER``
+    (the mean taken off, the variance the mean of the squared deviations, no bias) and gain a float32 vector of the
+    row's width (None with ``NORM_NONE``).  With ``rows`` only those rows are computed and the residual is not written.
+    ``want_out`` False: only the sum is wanted and nothing is returned."""
+    dim = residual.shape[1]
+    n = rows.shape[0] if rows is not None else residual.shape[0]
+    if residual.dtype != torch.float32:
+        raise KernelError("the residual stream is float32")
+    if delta is not None and delta.dtype != out_dtype:
+        raise KernelError(f"sublayer output is {delta.dtype}, compute dtype is {out_dtype}")
+    post_mode, post_gain, post_eps = post if post is not None else (NORM_NONE, None, 0.0)
+    out_mode, gain, eps = out_norm if out_norm is not None else (NORM_NONE, None, 0.0)
+    for g in (post_gain, gain):
+        if g is not None and (g.dtype != torch.float32 or g.shape[0] != dim):
+            raise KernelError("normed_add_norm: gains are float32 vectors of the row's width")
+    out = torch.empty((n, dim), dtype=out_dtype, device=residual.device) if want_out else None
+    _call("elementwise", "fms_normed_add_norm", _ptr(residual), _ptr(delta), int(post_mode), _ptr(post_gain), float(post_eps),
+          int(out_mode), _ptr(gain), float(eps), _ptr(out), _code(out_dtype), _ptr(rows), n, dim, residual.shape[0], _stream())
     return out
 
 
@@ -530,18 +560,25 @@ def attention_constants(head_dim: int, dtype: torch.dtype, nheads: int, kvheads:
 
 def qk_prepare_store(proj: torch.Tensor, inv_freq: Optional[torch.Tensor], rot: int, qk_norm: bool, eps: float, batch,
                      view, nheads: int, kvheads: int, dim: int, vdim: int, pad: int,
-                     writes_cache: bool = True) -> torch.Tensor:
+                     writes_cache: bool = True, norm_first: bool = False, q_gain: Optional[torch.Tensor] = None,
+                     k_gain: Optional[torch.Tensor] = None, halves: bool = False, values_are_keys: bool = False) -> torch.Tensor:
     """From rows [q: nheads x dim | k: kvheads x dim | v: kvheads x vdim | ...] of ``proj``: rotates the first ``rot``
-    values of every q and k head by the row's position (adjacent pairs), divides q and k by their root mean square
-    over ``dim`` where ``qk_norm``, writes k and v into the cache (heads of ``pad`` values there, zeros beyond dim and
-    vdim) and returns q [tokens, nheads * pad], padded alike."""
+    values of every q and k head by the row's position (adjacent pairs; with ``halves`` value i with value i + rot / 2),
+    divides q and k by their root mean square over ``dim`` where ``qk_norm`` (after the rotation; with ``norm_first``
+    before it, and then times ``q_gain`` / ``k_gain``, float32 [dim], where given), writes k and v into the cache (heads
+    of ``pad`` values there, zeros beyond dim and vdim) and returns q [tokens, nheads * pad], padded alike.
+    ``values_are_keys``: the rows have no v columns; a value is its key as projected, before norm and rotation."""
     n = proj.shape[0]
+    for g in (q_gain, k_gain):
+        if g is not None and (g.dtype != torch.float32 or g.shape[0] != dim):
+            raise KernelError("qk_prepare_store: gains are float32 vectors of the head's size")
     if view.keys.dtype != proj.dtype or view.keys.shape[-1] != pad:
         raise KernelError(f"cache is {view.keys.dtype} with heads of {view.keys.shape[-1]}, activations are {proj.dtype}, "
                           f"heads of {pad}")
     q = torch.empty((n, nheads * pad), dtype=proj.dtype, device=proj.device)
     _call("elementwise", "fms_qk_prepare_store", _ptr(proj), _code(proj.dtype), proj.shape[1], _ptr(q), _ptr(inv_freq),
-          int(rot), 1 if qk_norm else 0, float(eps), _ptr(batch.positions), _ptr(getattr(batch, "position_ids", None)),
+          int(rot), 1 if qk_norm else 0, float(eps), _ptr(q_gain), _ptr(k_gain), 1 if norm_first else 0, 1 if halves else 0,
+          1 if values_are_keys else 0, _ptr(batch.positions), _ptr(getattr(batch, "position_ids", None)),
           _ptr(batch.token_seq), _ptr(batch.slots), _ptr(view.keys), _ptr(view.values), _ptr(view.table),
           view.table.shape[1], view.block_tokens, n, nheads, kvheads, dim, vdim, pad, 1 if writes_cache else 0,
           _ptr(error_flag(proj.device)), batch.slots.shape[0], view.table.shape[0], view.keys.shape[0], _stream())
@@ -549,15 +586,15 @@ def qk_prepare_store(proj: torch.Tensor, inv_freq: Optional[torch.Tensor], rot: 
 
 
 def sigmoid_gate(o: torch.Tensor, gate: Optional[torch.Tensor], gate_offset: int, nheads: int, vdim: int, pad: int,
-                 factor: float = 1.0) -> torch.Tensor:
+                 factor: float = 1.0, per_head: bool = False) -> torch.Tensor:
     """out[t, h, :vdim] = factor * o[t, h, :vdim] * sigmoid(gate[t, gate_offset + h * vdim + :vdim]) for o with heads
     of ``pad`` values; ``gate`` is a matrix whose columns from ``gate_offset`` on hold the gates' logits (None: no
-    gate, only the padding is dropped)."""
+    gate, only the padding is dropped).  ``per_head``: one gate a head, sigmoid(gate[t, gate_offset + h])."""
     n = o.shape[0]
     out = torch.empty((n, nheads * vdim), dtype=o.dtype, device=o.device)
     gate_ptr = None if gate is None else _ptr(gate) + gate_offset * gate.element_size()
     _call("elementwise", "fms_sigmoid_gate", _ptr(o), gate_ptr, 0 if gate is None else gate.shape[1], _ptr(out),
-          _code(o.dtype), n, nheads, vdim, pad, float(factor), _stream())
+          _code(o.dtype), n, nheads, vdim, pad, float(factor), 1 if per_head else 0, _stream())
     return out
 
 
@@ -704,6 +741,53 @@ def delta_rule_scan(qkv: torch.Tensor, proj: torch.Tensor, beta_offset: int, a_r
           batch.n_seqs, heads, kvheads, dim, vdim, 1 if writes_state else 0, state.shape[0], _stream())
     global launches
     launches += 1  # the kernel that makes q, k, the decays and the betas ready
+    return o
+
+
+ACT_NONE, ACT_SILU = 0, 1
+
+
+def decay_scan(proj: torch.Tensor, state: torch.Tensor, batch, heads: int, dim: int, vdim: int, activation: int = ACT_NONE,
+               q_scale: float = 1.0, decay: Optional[torch.Tensor] = None, gate_offset: int = 0,
+               gate_bias: Optional[torch.Tensor] = None, gate_cap: float = 0.0, norm_state: Optional[torch.Tensor] = None,
+               writes_state: bool = True) -> torch.Tensor:
+    """A state matrix per head under scalar decays, over each sequence's rows.  The first columns of ``proj`` are
+    [q: heads x dim | k: heads x dim | v: heads x vdim]; they are taken in float32 through ``activation`` (``ACT_SILU``
+    or none), q times ``q_scale``.  ``state`` float32 [slots, heads, vdim, dim].
+
+    With ``decay`` (float32 [heads]): S = decay_h S + k v^T; o = S^T q.
+
+    With ``gate_bias`` (float32 [2 heads]: the input gates' biases, then the forget gates'): columns ``gate_offset + h``
+    and ``gate_offset + heads + h`` of ``proj`` are head h's gates before their biases, i = cap tanh((. + b) / cap),
+    f = logsigmoid(cap tanh((. + b) / cap)); with the running maximum m' = max(f + m, i): S = exp(f + m - m') S +
+    exp(i - m') k v^T, n likewise with k alone, o = S^T q / (max(|n.q|, exp(-m')) + 1e-6).  ``norm_state`` float32
+    [slots, heads, dim + 1] holds n and then m (zeros for a new sequence).
+
+    Returns o float32 [tokens, heads * vdim]."""
+    n = proj.shape[0]
+    cols = heads * (2 * dim + vdim)
+    gated = gate_bias is not None
+    if state.dtype != torch.float32 or tuple(state.shape[1:]) != (heads, vdim, dim) or proj.shape[1] < cols:
+        raise KernelError("decay_scan: proj [tokens, q | k | v | ...], state float32 [slots, heads, vdim, dim]")
+    if gated == (decay is not None):
+        raise KernelError("decay_scan: either one decay a head or the gates' biases")
+    if gated and (norm_state is None or norm_state.dtype != torch.float32 or tuple(norm_state.shape[1:]) != (heads, dim + 1)
+                  or gate_bias.dtype != torch.float32 or gate_bias.shape[0] != 2 * heads
+                  or proj.shape[1] < gate_offset + 2 * heads or norm_state.shape[0] != state.shape[0]):
+        raise KernelError("decay_scan: gate biases float32 [2 heads], norm_state float32 [slots, heads, dim + 1]")
+    if not gated and (decay.dtype != torch.float32 or decay.shape[0] != heads):
+        raise KernelError("decay_scan: decays float32 [heads]")
+    qkv = torch.empty((n, cols), dtype=torch.float32, device=proj.device)
+    _call("state_scan", "fms_linear_prepare", _ptr(proj), _code(proj.dtype), proj.shape[1], _ptr(qkv), n, cols, heads * dim,
+          float(q_scale), int(activation), _stream())
+    o = torch.empty((n, heads * vdim), dtype=torch.float32, device=proj.device)
+    gates = torch.empty((n, heads, 3), dtype=torch.float32, device=proj.device) if gated else None
+    gate_ptr = _ptr(proj) + gate_offset * proj.element_size() if gated else None
+    _call("state_scan", "fms_decay_scan", _ptr(qkv), gate_ptr, _code(proj.dtype), proj.shape[1], _ptr(gate_bias),
+          float(gate_cap), _ptr(gates), _ptr(decay), _ptr(state), _ptr(norm_state), _ptr(o), _ptr(batch.first_row),
+          _ptr(batch.slots), n, batch.n_seqs, heads, dim, vdim, 1 if writes_state else 0, state.shape[0], _stream())
+    global launches
+    launches += 1 if gated else 0  # the kernel that walks the gates
     return o
 
 

@@ -136,6 +136,7 @@ def get_model(architecture: str, variant: Optional[str] = None, model_path: Opti
 from . import llama  # noqa: E402,F401  (registers the architecture and its variants)
 from . import goletar  # noqa: E402,F401
 from . import niletar  # noqa: E402,F401
+from . import figonex  # noqa: E402,F401
 
 
 def _import_plugins() -> None:

@@ -72,13 +72,20 @@ class MultiHeadAttention(Part):
 class SinkAttention(Part):
     """``sink_attention``: grouped-query softmax attention over the cache with, each of them optional,
 
-        rotation of only the first ``rot_dims`` values of every head (adjacent pairs; ``position`` gives base and scaling)
-        q and k divided by their root mean square over the head, after the rotation (``qk_norm``, eps ``eps``; no gain)
-        a learned sink per head in the softmax's denominator: p_j = exp(s_j) / (sum_i exp(s_i) + exp(sink_h))   (``sink``)
-        a gate on the heads' results before the output projection: o * sigmoid(Wg h)                            (``gate``)
-        values of another size than keys (``vdim``)
+        rotation of only the first ``rot_dims`` values of every head (adjacent pairs; ``position`` gives base and scaling;
+            ``pairing`` "halves": value i turns with value i + rot_dims / 2 instead)
+        q and k divided by their root mean square over the head, after the rotation (``qk_norm``, eps ``eps``; no gain);
+            ``qk_norm`` "before": the norm comes before the rotation and has gains ``q_norm`` and ``k_norm`` [head_dim],
+            each shared by all heads
+        a learned sink per head in the softmax's denominator: p_j = exp(s_j) / (sum_i exp(s_i) + exp(sink_h))   (``sink``);
+            ``sink_logit``: a fixed number in the place of the learned ones (0.0: one added to the denominator)
+        a gate on the heads' results before the output projection: o * sigmoid(Wg h) (``gate``), one gate a value, or
+            with ``gate`` "head" one a head
+        values of another size than keys (``vdim``); ``values`` "keys": no value projection, a value is its key as
+            projected, before norm and rotation
 
-    [Wq; Wk; Wv; Wg] is one fused projection (``in_proj``; bias [bq; bk; bv; 0] where ``bias``).  The cache holds heads
+    [Wq; Wk; Wv; Wg] is one fused projection (``in_proj``; bias [bq; bk; bv; 0] where ``bias``; without Wv where the
+    values are the keys; its rows filled up with zeros to a multiple of 8 where the gates are one a head).  The cache holds heads
     of ``pad`` = max(head_dim, vdim) rounded up to 16 values, zeros beyond each one's own size, so that the attention
     kernels built for one head size serve keys and values alike; q is padded the same way and the padding of the
     result is dropped by the gate kernel.  ``out_factor`` multiplies the result before the output projection (a mixer
@@ -98,18 +105,41 @@ class SinkAttention(Part):
         if self.rot_dims % 2 or not (0 <= self.rot_dims <= self.head_dim):
             raise ValueError(f"sink_attention: {self.rot_dims} rotated values of {self.head_dim}")
         self.qk_norm, self.eps = bool(o.get("qk_norm", False)), float(o.get("eps", 1e-6))
+        self.norm_first = o.get("qk_norm") == "before"
+        self.halves = o.get("pairing", "adjacent") == "halves"
+        if o.get("pairing", "adjacent") not in ("adjacent", "halves") or o.get("values", "projected") not in ("projected", "keys"):
+            raise ValueError(f"sink_attention: pairing {o.get('pairing')!r}, values {o.get('values')!r}")
+        self.values_are_keys = o.get("values", "projected") == "keys"
+        if self.values_are_keys and self.vdim != self.head_dim:
+            raise ValueError(f"sink_attention: values that are the keys have their size, {self.head_dim}, not {self.vdim}")
+        self.sink_logit = None if o.get("sink_logit") is None else float(o["sink_logit"])
         self.has_sink, self.has_gate = bool(o.get("sink", False)), bool(o.get("gate", False))
+        self.gate_per_head = o.get("gate") == "head"
+        if self.has_sink and self.sink_logit is not None:
+            raise ValueError("sink_attention: either learned sinks or one fixed logit")
         self.out_factor = float(o.get("out_factor", 1.0))
         self.scale = 1.0 / math.sqrt(spec.head_dim) if spec.scale is None else float(spec.scale)
         self.window = int(spec.window)
         self.position_spec = spec.position
-        self.gate_col = (self.nheads + self.kvheads) * self.head_dim + self.kvheads * self.vdim
-        rows = self.gate_col + (self.nheads * self.vdim if self.has_gate else 0)
+        self.gate_col = (self.nheads + self.kvheads) * self.head_dim + (0 if self.values_are_keys else self.kvheads * self.vdim)
+        rows = self.fused_rows(self.nheads, self.kvheads, self.head_dim, self.vdim, self.values_are_keys,
+                               o.get("gate", False))
         self.in_proj = self.add("in_proj", Linear(spec.dim, rows, spec.bias))
         if self.has_sink:
             self.declare("sink", (self.nheads,), role="vector")
+        if self.norm_first:
+            self.declare("q_norm", (self.head_dim,), role="vector")
+            self.declare("k_norm", (self.head_dim,), role="vector")
         self.dense = self.add("dense", Linear(self.nheads * self.vdim, spec.dim, False))
-        self._inv_freq = self._sink = None
+        self._inv_freq = self._sink = self._q_gain = self._k_gain = None
+
+    @staticmethod
+    def fused_rows(nheads: int, kvheads: int, head_dim: int, vdim: int, values_are_keys: bool, gate) -> int:
+        """Rows of the fused projection [q; k; v; g]: what a checkpoint adapter has to put together."""
+        rows = (nheads + kvheads) * head_dim + (0 if values_are_keys else kvheads * vdim)
+        if gate == "head":
+            return (rows + nheads + 7) // 8 * 8
+        return rows + (nheads * vdim if gate else 0)
 
     def finalize(self, device, dtype) -> None:
         super().finalize(device, dtype)
@@ -122,6 +152,11 @@ class SinkAttention(Part):
             self._inv_freq = f.to(torch.float32).to(device).contiguous()
         if self.has_sink:
             self._sink = self.tensor("sink").float().contiguous()
+        elif self.sink_logit is not None:
+            self._sink = torch.full((self.nheads,), self.sink_logit, dtype=torch.float32, device=device)
+        if self.norm_first:
+            self._q_gain = self.tensor("q_norm").float().contiguous()
+            self._k_gain = self.tensor("k_norm").float().contiguous()
 
     def cache_request(self):
         return KVRequest(self.kvheads, self.pad, self.window)
@@ -130,10 +165,12 @@ class SinkAttention(Part):
         """The gated heads' results [tokens, nheads * vdim], before the output projection."""
         proj = self.in_proj.forward(x)
         q = ops.qk_prepare_store(proj, self._inv_freq, self.rot_dims, self.qk_norm, self.eps, batch, cache_view,
-                                 self.nheads, self.kvheads, self.head_dim, self.vdim, self.pad, writes_cache)
+                                 self.nheads, self.kvheads, self.head_dim, self.vdim, self.pad, writes_cache,
+                                 norm_first=self.norm_first, q_gain=self._q_gain, k_gain=self._k_gain, halves=self.halves,
+                                 values_are_keys=self.values_are_keys)
         o = ops.attention(q, batch, cache_view, self.nheads, self.kvheads, self.pad, self.scale, self.window, self._sink)
         return ops.sigmoid_gate(o, proj if self.has_gate else None, self.gate_col, self.nheads, self.vdim, self.pad,
-                                self.out_factor)
+                                self.out_factor, self.gate_per_head)
 
     def forward(self, x, batch, cache_view, writes_cache: bool = True):
         return self.dense.forward(self.heads_out(x, batch, cache_view, writes_cache))

@@ -19,6 +19,10 @@ read the stream itself, and what the block hands on is a ``StreamCopy`` (nothing
 x += post2(feed_forward(pre2(x))).  What it hands on as pending is a ``NormedDelta``: the next norm (this layer's, the
 next layer's or the decoder's last) norms it, adds it and takes its own norm in one kernel.  A layer without a
 feed-forward ends after its mixer.
+
+``OutputNormBlock`` ("output_norm"): a norm on each sublayer's output only, x += norm1(mixer(x));
+x += norm2(feed_forward(x)); the sublayers read the stream itself.  What it hands on is a ``NormedDelta`` as well; the
+kernel that adds it also leaves the summed stream in the compute dtype for the sublayer that reads it next.
 """
 from __future__ import annotations
 
@@ -128,7 +132,49 @@ class PostNormBlock(Part):
         return super().kernel_libraries(dtype) + ["elementwise"]
 
 
+class OutputNormBlock(Part):
+    """``output_norm``: x += norm1(mixer(x)); x += norm2(feed_forward(x)), with no norm in front of a sublayer.  The
+    norms need ``add(residual, delta, dtype)`` (``LayerNorm`` has it).  A layer without a feed-forward ends after its
+    mixer.  The last sublayer's output stays pending with its norm, so that whatever comes next (this arrangement's
+    next layer, or the decoder's last norm) adds it in the kernel that it runs anyway."""
+
+    def __init__(self, spec: BlockSpec) -> None:
+        super().__init__()
+        n_mixer_norm, n_mixer, n_ff_norm, n_ff = spec.names
+        self.mixer = self.add(n_mixer, build_mixer(spec.mixer))
+        self.mixer_norm = self.add(n_mixer_norm, build_norm(spec.mixer_norm))
+        self.feed_forward = None
+        if spec.feed_forward is not None:
+            if spec.feed_forward_norm is None:
+                raise ValueError("an output-norm layer with a feed-forward needs the norm of its output")
+            self.feed_forward = self.add(n_ff, build_feed_forward(spec.feed_forward))
+            self.feed_forward_norm = self.add(n_ff_norm, build_norm(spec.feed_forward_norm))
+
+    def cache_request(self):
+        return self.mixer.cache_request()
+
+    def forward(self, residual, pending, batch, cache_view, writes_cache, dtype):
+        if isinstance(pending, NormedDelta) and hasattr(pending.norm, "add"):
+            h = pending.norm.add(residual, pending.delta, dtype)
+        elif isinstance(pending, StreamCopy):
+            h = pending.rows
+        elif pending is None:
+            h = ops.cast_rows(residual, dtype)
+        else:
+            raise ValueError("an output-norm layer follows a layer whose pending output it cannot add: only a normed "
+                             "output whose norm has add(), or an up-to-date stream, may come before it")
+        a = self.mixer.forward(h, batch, cache_view, writes_cache)
+        if self.feed_forward is None:
+            return NormedDelta(a, self.mixer_norm)
+        h = self.mixer_norm.add(residual, a, dtype)
+        return NormedDelta(self.feed_forward.forward(h), self.feed_forward_norm)
+
+    def kernel_libraries(self, dtype):
+        return super().kernel_libraries(dtype) + ["elementwise"]
+
+
 Block = PreNormBlock  # the name under which earlier callers know it
+register_block("output_norm", OutputNormBlock)
 register_block("post_norm", PostNormBlock)
 register_block("pre_norm", PreNormBlock)
 register_block("sandwich", SandwichBlock)

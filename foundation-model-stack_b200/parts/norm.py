@@ -18,8 +18,16 @@ d = post_norm(delta); residual += d; out = norm(residual), all float32.
 ``ScalarRMSNorm`` ("rmsnorm_scalar"): y = g * x / sqrt(mean(x^2) + eps) with ONE number g for the whole row (a tensor
 without dimensions in the checkpoint).  The number is read once when the weights are loaded and handed to the kernel
 by value.
+
+``LayerNorm`` ("layernorm"): y = (x - mean(x)) / sqrt(mean((x - mean(x))^2) + eps) * w, no bias.  Option
+``layer_scale``: a second vector ``scale`` multiplies the result element by element (the gain the kernel sees is
+w * scale, taken in float32 once).  It norms a sublayer's output on its way into the stream (as the ``norm`` of a
+``NormedDelta``), and as a norm of the stream itself it adds what is pending and norms the sum in one kernel; with
+``mode_and_gain() == None`` in the place of a norm, the same kernel hands the summed stream on in the compute dtype.
 """
 from __future__ import annotations
+
+import torch
 
 from ..config.specs import NormSpec
 from ..kernels import ops
@@ -117,5 +125,50 @@ class ScalarRMSNorm(Part):
         return ["elementwise"]
 
 
+class LayerNorm(Part):
+    def __init__(self, spec: NormSpec) -> None:
+        super().__init__()
+        self.dim = spec.dim
+        self.eps = float(spec.eps)
+        self.layer_scale = bool(dict(spec.options).get("layer_scale", False))
+        self.declare("weight", (spec.dim,), role="vector")
+        if self.layer_scale:
+            self.declare("scale", (spec.dim,), role="vector")
+        self._gain = None
+
+    def finalize(self, device, dtype) -> None:
+        super().finalize(device, dtype)
+        g = self.tensor("weight").float()
+        if self.layer_scale:
+            g = g * self.tensor("scale").float()
+        self._gain = g.contiguous()
+
+    def mode_and_gain(self):
+        """(mode, float32 gain vector, eps): what ``ops.normed_add_norm`` takes for either of its two norms."""
+        return ops.NORM_LAYER, self._gain, self.eps
+
+    def add(self, residual, delta, out_dtype):
+        """residual += this norm of ``delta`` (a sublayer's output), in float32; returns the stream in ``out_dtype``
+        (the stream itself where that is float32)."""
+        if out_dtype == torch.float32:
+            ops.normed_add_norm(residual, delta, self.mode_and_gain(), None, out_dtype, want_out=False)
+            return residual
+        return ops.normed_add_norm(residual, delta, self.mode_and_gain(), None, out_dtype)
+
+    def apply(self, residual, delta, out_dtype, rows=None):
+        post = None
+        if isinstance(delta, StreamCopy):
+            delta = None
+        if isinstance(delta, NormedDelta):
+            if not hasattr(delta.norm, "mode_and_gain"):
+                raise ValueError("a layer norm adds a pending output that is normed by a norm with mode_and_gain()")
+            delta, post = delta.delta, delta.norm.mode_and_gain()
+        return ops.normed_add_norm(residual, delta, post, self.mode_and_gain(), out_dtype, rows)
+
+    def kernel_libraries(self, dtype):
+        return ["elementwise"]
+
+
+register_norm("layernorm", LayerNorm)
 register_norm("rmsnorm", RMSNorm)
 register_norm("rmsnorm_scalar", ScalarRMSNorm)

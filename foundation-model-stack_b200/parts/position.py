@@ -43,6 +43,8 @@ def rotary_inverse_frequencies(head_dim: int, theta: float, scaling: dict, dtype
     kind = scaling.get("rope_type", scaling.get("type", "regular")) if scaling else "regular"
     if kind in ("regular", "default", None):
         return inv
+    if kind == "linear":  # every frequency divided by one factor
+        return inv / float(scaling["factor"])
     if kind == "llama3":
         factor = float(scaling["factor"])
         low = float(scaling["low_freq_factor"])
@@ -54,7 +56,7 @@ def rotary_inverse_frequencies(head_dim: int, theta: float, scaling: dict, dtype
         blended = (1 - smooth) * slowed / factor + smooth * slowed
         medium = ~(wavelen < old / high) * ~(wavelen > old / low)
         return torch.where(medium, blended, slowed)
-    raise ValueError(f"rope scaling {kind!r} is not supported (supported: regular, llama3)")
+    raise ValueError(f"rope scaling {kind!r} is not supported (supported: regular, linear, llama3)")
 
 
 class PositionEncoding(Part):
