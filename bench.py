@@ -680,6 +680,115 @@ def run_niletar(args):
 
 
 # --------------------------------------------------------------------------------------------------
+# --compare figonex: the Figonex design beside Llama at equal width, layer for layer
+# --------------------------------------------------------------------------------------------------
+FIGONEX_SHAPE = dict(width=4096, vocab=128256, ff=14336, heads=32, kv_heads=8, dim=128, rot_dims=64,
+                     memory_heads=32, memory_dim=128, memory_vdim=128, gate_cap=15.0)
+
+
+def figonex_layers(kinds, with_mlp=True):
+    from fms_b200.models.figonex import attention_layer, dense_mlp, lightning_layer, mlstm_layer
+
+    g = FIGONEX_SHAPE
+    mlp = dense_mlp(g["ff"]) if with_mlp else None
+    h = g["memory_heads"]
+    decays = [1.0 - 0.1 * 0.01 ** (i / max(1, h - 1)) for i in range(h)]
+    make = {"mlstm": lambda: mlstm_layer(h, g["memory_dim"], g["memory_vdim"], g["gate_cap"], mlp),
+            "attention": lambda: attention_layer(g["heads"], g["kv_heads"], g["dim"], g["rot_dims"], 500000.0, None,
+                                                 g["dim"] ** -0.5, mlp),
+            "lightning": lambda: lightning_layer(h, g["memory_dim"], g["memory_vdim"], decays, mlp)}
+    return [make[k]() for k in kinds]
+
+
+def figonex_counts(layers, tokens, batch_context, batch):
+    """(flops of a prompt of `tokens`, bytes a decode step of `batch` sequences with `batch_context` cached tokens
+    reads and writes) of the given layers: products, attention over the cache (keys and values are cached apart: a
+    value is its key before norm and rotation), the scans of the matrix memories (6 flops per state value and token:
+    they run in float32 on the CUDA cores), the states of the sequences (read and written once a step)."""
+    g = FIGONEX_SHAPE
+    d, flops, moved = g["width"], 0.0, 0.0
+    for layer in layers:
+        m = layer["mixer"]
+        h, k = m["heads"], m["dim"]
+        if layer["type"] == "attention":
+            w = d * (h * k + m["kv_heads"] * k + h) + h * k * d
+            flops += 2.0 * tokens * tokens * h * k  # the causal half of 4 T^2 per head and value
+            moved += 2 * 2 * batch_context * m["kv_heads"] * k
+        else:
+            v = m["vdim"]
+            w = d * (2 * h * k + 2 * h * v + (2 * h if layer["type"] == "mlstm" else 0)) + h * v * d
+            flops += 6.0 * tokens * h * k * v
+            moved += 2 * 4 * batch * h * k * v
+        if layer.get("mlp"):
+            w += 3 * layer["mlp"]["ff"] * d
+        flops += 2.0 * tokens * w
+        moved += 2 * w
+    head = 2 * g["vocab"] * d
+    return flops + head, moved + head
+
+
+class FigonexMeasured(Measured):
+    """A Figonex model of given layers on the device, measured like the Llama one."""
+
+    def __init__(self, layers, room, max_prompt, slots):
+        import torch
+
+        from fms_b200.models.figonex import Figonex, FigonexConfig
+        from fms_b200.weights.sources import RandomSource
+
+        g = FIGONEX_SHAPE
+        self.m, self.dtype, self.nlayers, self.itemsize, self.layers = dict(vocab=g["vocab"]), "bf16", len(layers), 2, layers
+        self.model = Figonex(FigonexConfig(vocab=g["vocab"], width=g["width"], embedding_scale=8.0, layers=layers))
+        self.model.load(RandomSource(self.model.checkpoint_layout(), 0, dtype=torch.bfloat16, device="cuda"), "native", "cuda",
+                        torch.bfloat16)
+        self.engine = self.model.new_engine(max_tokens=slots * (max_prompt + 2 * room + 128), max_slots=slots)
+        self.torch = torch
+
+
+def run_figonex(args):
+    """One JSON line: prompts of 512 and 2,048 tokens and decode steps of 1, 8 and 64 sequences, for `--layers` layers
+    (default 4) of the Figonex design at the width of the benchmark's Llama (a gated matrix memory, attention,
+    attention, a decaying matrix memory, each with the dense feed-forward of 14,336), for as many Llama-3-8B layers, and
+    for each of Figonex's mixers alone (models of one kind of layer without a feed-forward).  Each figure with its
+    fraction of the measured peak: flops of a prompt over the bf16 product peak, bytes a decode step moves over the copy
+    peak."""
+    pk = peaks()
+    n = args.layers or 4
+    steps, warm = max(16, args.steps // 2), max(3, args.warmup // 2)
+    room = warm + 3 * steps + 8
+    lengths = {1: [1024], 8: [1024] * 8, 64: [1024] * 64}
+    out = {"compare": "figonex", "layers": n, "shape": FIGONEX_SHAPE, "peaks": pk, "steps": steps, "warmup": warm, "models": {}}
+
+    def measure(run, name, flops_bytes):
+        row = {}
+        for tokens in (512, 2048):
+            ms = run.prefill(tokens, 3)
+            row[f"prefill_{tokens}"] = {"ms": round(ms, 3), "tok_s": round(tokens / (ms / 1e3), 1),
+                                        "frac_of_bf16_peak": round(flops_bytes(tokens, 0, 0)[0] / (ms / 1e3) / 1e12 / pk["bf16_tflops"], 4)}
+        for b in (1, 8, 64):
+            v, ms, ctx, _, _ = run.device_decode(b, steps, warm, lengths[b], regions=3)
+            row[f"decode_b{b}"] = {"ms": round(ms, 4), "tok_s": round(v, 1),
+                                   "frac_of_copy_peak": round(flops_bytes(0, ctx, b)[1] / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 4)}
+        out["models"][name] = row
+        run.close()
+
+    order = ("mlstm", "attention", "attention", "lightning")
+    variants = [("figonex", figonex_layers([order[i % 4] for i in range(n)])),
+                ("mlstm_only", figonex_layers(["mlstm"] * n, False)),
+                ("attention_only", figonex_layers(["attention"] * n, False)),
+                ("lightning_only", figonex_layers(["lightning"] * n, False))]
+    if args.only:
+        variants = [v for v in variants if v[0] == args.only]
+    for name, layers in variants:
+        measure(FigonexMeasured(layers, room, 2048, 64), name,
+                lambda tokens, ctx, b, layers=layers: figonex_counts(layers, tokens, ctx, b))
+    if not args.only or args.only == "llama":
+        llama = Measured(MODEL, "bf16", n, room, 2048, slots=64)
+        measure(llama, "llama", lambda tokens, ctx, b: (prefill_flops(n, tokens), decode_bytes(n, ctx)))
+    print(json.dumps(out))
+
+
+# --------------------------------------------------------------------------------------------------
 # the reference, unmodified, through its own public API
 # --------------------------------------------------------------------------------------------------
 def run_reference(args):
@@ -777,10 +886,11 @@ def main():
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="with --only prefill: the prompt's length")
     ap.add_argument("--points", choices=["default", "main", "long"], default="default",
                     help="main: without the further configurations; long: also decode at batch 64 with 8k contexts")
-    ap.add_argument("--compare", choices=["", "goletar", "niletar"], default="",
+    ap.add_argument("--compare", choices=["", "goletar", "niletar", "figonex"], default="",
                     help="goletar: the Goletar design beside as many Llama layers of equal width (--layers, default 4; "
                     "--only goletar|mingru_only|latent_attention_only|mingru_with_experts|llama for one of them); "
-                    "niletar: the Niletar design likewise (--only niletar|parallel_only|mamba2_only|llama)")
+                    "niletar: the Niletar design likewise (--only niletar|parallel_only|mamba2_only|llama); "
+                    "figonex: the Figonex design likewise (--only figonex|mlstm_only|attention_only|lightning_only|llama)")
     args = ap.parse_args()
     choose_model(args.model)
     if args.gpus != 1:
@@ -791,6 +901,8 @@ def main():
         run_goletar(args)
     elif args.compare == "niletar":
         run_niletar(args)
+    elif args.compare == "figonex":
+        run_figonex(args)
     elif args.impl == "reference":
         run_reference(args)
     elif args.only in ("gemm_rows", "attention_prefill", "attention_decode"):
