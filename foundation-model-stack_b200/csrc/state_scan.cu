@@ -15,7 +15,7 @@
 //                       a and b from exponential gates under a running maximum m (m' = max(f + m, i), a = exp(f + m - m'),
 //                       b = exp(i - m')), a normalizer n = a n + b k and o = S^T q / (max(|n.q|, exp(-m')) + 1e-6);
 //                       linear_prepare makes q, k, v float32 (an activation, a factor on q), exp_gates walks the maxima
-//                       and the normalizer and leaves (a, b, 1 / denominator) for every token
+//                       and leaves (a, b, exp(-m')) for every token; the scan carries n beside its state columns
 //   gated_group_rmsnorm rows cut into groups, each divided by its own root mean square, times a weight; a gate
 //                       multiplies either before the norm (silu) or after it (sigmoid)
 //
@@ -533,21 +533,18 @@ __global__ void linear_prepare_kernel(const T* proj, int stride, float* out, int
   else out[i] = v[0];
 }
 
-// Exponential gates under a running maximum with their normalizer, a warp per (sequence, head).  gate_raw: column h
-// of the rows is head h's input gate before its bias, column heads + h its forget gate; bias [2 heads] float32; cap > 0:
+// Exponential gates under a running maximum, a warp per (sequence, head).  gate_raw: column h of the rows is head h's
+// input gate before its bias, column heads + h its forget gate; bias [2 heads] float32; cap > 0:
 //   i = cap tanh((raw_i + bias_i) / cap);  f = logsigmoid(cap tanh((raw_f + bias_f) / cap))
-//   m' = max(f + m, i);  a = exp(f + m - m');  b = exp(i - m');  n' = a n + b k
-//   gates[t, h] = (a, b, 1 / (max(|n'.q|, exp(-m')) + 1e-6))
-// norm_state holds per slot and head the normalizer n (dim values) and then m, zeros for a new sequence; both are left
-// at their values after the step's last row.  q and k are read from qkv (float32 rows q | k | v, head by head).  The
-// lanes take a token each for the gates and exponentials; maxima and normalizer are walked in order by the whole warp,
-// a lane holding every 32nd value of n.  No other kernel touches norm_state, so nothing of it is read while it changes.
-constexpr int GATE_RUNS = 8;  // dim <= 32 * GATE_RUNS
-
+//   m' = max(f + m, i);  a = exp(f + m - m');  b = exp(i - m');  gates[t, h] = (a, b, exp(-m'))
+// norm_state holds per slot and head the normalizer n (dim values) and then m, zeros for a new sequence.  m is left at
+// its value after the step's last row; n as it was before the step is copied to norm_in [sequences, heads, dim], from
+// where every block of the scan reads it (the scan's blocks do not all run at once, and one of them writes the new n
+// into norm_state).  The lanes take a token each for the gates and exponentials; the maxima are walked in order.
 template <typename T>
-__global__ void exp_gates_kernel(const T* gate_raw, int stride, const float* bias, float cap, const float* qkv, int row_w,
-                                 float* norm_state, float* gates, const int* first_row, const int* slots, int heads,
-                                 int dim, int write_state, int n_seqs, int n_slots) {
+__global__ void exp_gates_kernel(const T* gate_raw, int stride, const float* bias, float cap, float* norm_state,
+                                 float* norm_in, float* gates, const int* first_row, const int* slots, int heads, int dim,
+                                 int write_state, int n_seqs, int n_slots) {
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31;
@@ -559,12 +556,8 @@ __global__ void exp_gates_kernel(const T* gate_raw, int stride, const float* bia
   const int lo = first_row[seq], hi = first_row[seq + 1];
   float* st = norm_state + ((size_t)slot * heads + head) * (dim + 1);
   float m = st[dim];
-  float n[GATE_RUNS];
-#pragma unroll
-  for (int r = 0; r < GATE_RUNS; ++r) n[r] = (r * 32 + lane < dim) ? st[r * 32 + lane] : 0.f;
+  for (int e = lane; e < dim; e += 32) norm_in[(size_t)unit * dim + e] = st[e];
   const float bi = bias[head], bf = bias[heads + head];
-  const float* qh = qkv + (size_t)head * dim;
-  const float* kh = qkv + (size_t)(heads + head) * dim;
   for (int base = lo; base < hi; base += 32) {
     const int t = base + lane;
     float gi = 0.f, gf = 0.f;
@@ -584,48 +577,29 @@ __global__ void exp_gates_kernel(const T* gate_raw, int stride, const float* bia
       }
       m = next;
     }
-    const float keep = expf(gf + before - after), take = expf(gi - after);
-    float nq = 0.f;
-#pragma unroll 4
-    for (int j = 0; j < cn; ++j) {
-      const float aj = __shfl_sync(0xffffffffu, keep, j), bj = __shfl_sync(0xffffffffu, take, j);
-      const size_t at = (size_t)(base + j) * row_w;
-      float part = 0.f;
-#pragma unroll
-      for (int r = 0; r < GATE_RUNS; ++r) {
-        if (r * 32 < dim) {
-          const int e = r * 32 + lane;
-          const float kk = e < dim ? kh[at + e] : 0.f, qq = e < dim ? qh[at + e] : 0.f;
-          n[r] = fmaf(aj, n[r], bj * kk);
-          part = fmaf(n[r], qq, part);
-        }
-      }
-      part = warp_sum(part);
-      if (lane == j) nq = part;
-    }
     if (t < hi) {
       float* g = gates + ((size_t)t * heads + head) * 3;
-      g[0] = keep;
-      g[1] = take;
-      g[2] = 1.f / (fmaxf(fabsf(nq), expf(-after)) + 1e-6f);
+      g[0] = expf(gf + before - after);
+      g[1] = expf(gi - after);
+      g[2] = expf(-after);
     }
   }
-  if (write_state) {
-#pragma unroll
-    for (int r = 0; r < GATE_RUNS; ++r)
-      if (r * 32 + lane < dim) st[r * 32 + lane] = n[r];
-    if (lane == 0) st[dim] = m;
-  }
+  if (write_state && lane == 0) st[dim] = m;
 }
 
 // qkv [tokens, 2 heads * dim + heads * vdim] float32: q | k | v, head by head; o [tokens, heads * vdim].
-// GATED: per token and head (a, b, c) in gates [tokens, heads, 3]: S = a S + b k v^T, o = c S^T q; else one decay a head
-// (decay [heads]): S = decay S + k v^T, o = S^T q.
+// GATED: per token and head (a, b, e) in gates [tokens, heads, 3]: S = a S + b k v^T, n = a n + b k,
+// o = S^T q / (max(|n.q|, e) + 1e-6).  Every thread walks its rows of n beside its rows of the state columns (n is
+// the state column of a value that is always one), so that a column group has n.q from the same shuffles as its sums
+// and no thread waits for another group; n before the step comes from norm_in [sequences, heads, dim], and the first
+// column group of a head's first block leaves the new n in norm_state [slots, heads, dim + 1].
+// Else one decay a head (decay [heads]): S = decay S + k v^T, o = S^T q.
 template <int NP, int VP, int PARTS, bool GATED>
 __global__ void __launch_bounds__(SCAN_THREADS) decay_scan_kernel(const float* qkv, const float* gates, const float* decay,
-                                                                  float* state, float* o, const int* first_row,
-                                                                  const int* slots, int heads, int dim, int vdim,
-                                                                  int write_state, int n_slots, int vec_qk, int vec_v) {
+                                                                  float* state, const float* norm_in, float* norm_state,
+                                                                  float* o, const int* first_row, const int* slots,
+                                                                  int heads, int dim, int vdim, int write_state,
+                                                                  int n_slots, int vec_qk, int vec_v) {
   constexpr int GROUPS = SCAN_THREADS / PARTS, NPAD = RowLayout<NP, PARTS>::ROW, RUN = RowLayout<NP, PARTS>::RUN, VB = GROUPS * VP;
   extern __shared__ __align__(16) float smem[];
   pdl_launch_dependents();
@@ -646,6 +620,8 @@ __global__ void __launch_bounds__(SCAN_THREADS) decay_scan_kernel(const float* q
     const int v = v0 + grp * VP + i;
     load_state<NP, PARTS>(state + (((size_t)slot * heads + head) * vdim + (v < vdim ? v : 0)) * dim, part, dim, v < vdim, s[i]);
   }
+  float nn[GATED ? NP : 1];
+  if constexpr (GATED) load_state<NP, PARTS>(norm_in + ((size_t)seq * heads + head) * dim, part, dim, true, nn);
   const float fixed = GATED ? 1.f : decay[head];
   __syncthreads();
   auto issue = [&](int c0, int stage) {
@@ -675,11 +651,12 @@ __global__ void __launch_bounds__(SCAN_THREADS) decay_scan_kernel(const float* q
       load_run<NP>(sk + t * NPAD + part * RUN, k);
       load_run<NP>(sq + t * NPAD + part * RUN, q);
       const float a = GATED ? sg[t * 4] : fixed;
-      float acc[VP], val[VP];
+      const float b = GATED ? sg[t * 4 + 1] : 1.f;
+      float acc[VP], val[VP], nq = 0.f;
 #pragma unroll
       for (int i = 0; i < VP; ++i) {
         acc[i] = 0.f;
-        val[i] = sv[t * VB + grp * VP + i] * (GATED ? sg[t * 4 + 1] : 1.f);
+        val[i] = sv[t * VB + grp * VP + i] * b;
       }
 #pragma unroll
       for (int j = 0; j < NP; ++j) {
@@ -689,8 +666,13 @@ __global__ void __launch_bounds__(SCAN_THREADS) decay_scan_kernel(const float* q
           s[i][j] = fmaf(a, s[i][j], kj * val[i]);
           acc[i] = fmaf(s[i][j], qj, acc[i]);
         }
+        if constexpr (GATED) {
+          nn[j] = fmaf(a, nn[j], kj * b);
+          nq = fmaf(nn[j], qj, nq);
+        }
       }
-      const float scale = GATED ? sg[t * 4 + 2] : 1.f;
+      float scale = 1.f;
+      if constexpr (GATED) scale = 1.f / (fmaxf(fabsf(group_sum<PARTS>(nq)), sg[t * 4 + 2]) + 1e-6f);
 #pragma unroll
       for (int i = 0; i < VP; ++i) {
         acc[i] = group_sum<PARTS>(acc[i]);
@@ -706,6 +688,14 @@ __global__ void __launch_bounds__(SCAN_THREADS) decay_scan_kernel(const float* q
       const int v = v0 + grp * VP + i;
       if (v >= vdim) continue;
       store_state<NP, PARTS>(state + (((size_t)slot * heads + head) * vdim + v) * dim, part, dim, s[i]);
+    }
+    if constexpr (GATED) {
+      if (blockIdx.z == 0 && grp == 0) {
+        float* st = norm_state + ((size_t)slot * heads + head) * (dim + 1);  // rows of dim + 1: no 16-byte stores
+#pragma unroll
+        for (int j = 0; j < NP; ++j)
+          if (part * NP + j < dim) st[part * NP + j] = nn[j];
+      }
     }
   }
 }
@@ -963,21 +953,22 @@ FMS_API int fms_linear_prepare(const void* proj, int dtype, int stride, float* o
 
 // qkv [tokens, 2 heads * dim + heads * vdim] float32.  With gate_raw (columns [i: heads | f: heads] of rows of
 // gate_stride values, bias [2 heads], cap): exponential gates, with normalizer and running maximum in norm_state
-// [slots, heads, dim + 1]; gates [tokens, heads, 3] is float32 scratch of the caller's.  Without: decay [heads].
+// [slots, heads, dim + 1]; gates [tokens, heads, 3] and norm_in [sequences, heads, dim] are float32 scratch of the
+// caller's.  Without: decay [heads].
 FMS_API int fms_decay_scan(const float* qkv, const void* gate_raw, int dtype, int gate_stride, const float* gate_bias,
-                           float cap, float* gates, const float* decay, float* state, float* norm_state, float* o,
+                           float cap, float* gates, float* norm_in, const float* decay, float* state, float* norm_state, float* o,
                            const int* first_row, const int* slots, int n_tokens, int n_seqs, int heads, int dim, int vdim,
                            int write_state, int n_slots, cudaStream_t stream) {
   if (n_seqs <= 0 || n_tokens <= 0) return 0;
   if (heads <= 0 || dim <= 0 || dim > 256 || vdim <= 0)
     return fms_fail("decay_scan: %d heads, dim %d (up to 256), vdim %d", heads, dim, vdim);
   const bool gated = gate_raw != nullptr;
-  if (gated && (!gate_bias || !gates || !norm_state || !(cap > 0.f))) return fms_fail("decay_scan: gates without bias, scratch, normalizer or cap");
+  if (gated && (!gate_bias || !gates || !norm_in || !norm_state || !(cap > 0.f))) return fms_fail("decay_scan: gates without bias, scratch, normalizer or cap");
   if (!gated && !decay) return fms_fail("decay_scan: neither gates nor decays");
   const long row_w = 2L * heads * dim + (long)heads * vdim;
   if (gated) {
     FMS_DISPATCH_DTYPE(dtype, T, fms_launch(exp_gates_kernel<T>, dim3((n_seqs * heads + 3) / 4), dim3(128), 0, stream,
-                                            (const T*)gate_raw, gate_stride, gate_bias, cap, qkv, (int)row_w, norm_state, gates,
+                                            (const T*)gate_raw, gate_stride, gate_bias, cap, norm_state, norm_in, gates,
                                             first_row, slots, heads, dim, write_state, n_seqs, n_slots));
   }
   const ScanShape shape = scan_shape(n_seqs, heads, vdim, dim);
@@ -990,7 +981,7 @@ FMS_API int fms_decay_scan(const float* qkv, const void* gate_raw, int dtype, in
     const size_t smem = ((size_t)2 * CH * (2 * RowLayout<NP, PARTS>::ROW + SCAN_THREADS / PARTS * VP + 4)) * sizeof(float); \
     cudaFuncSetAttribute(decay_scan_kernel<NP, VP, PARTS, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
     fms_launch(decay_scan_kernel<NP, VP, PARTS, GATED>, grid, block, smem, stream, qkv, (const float*)gates, decay, state, \
-               o, first_row, slots, heads, dim, vdim, write_state, n_slots, vec_qk, vec_v);                               \
+               (const float*)norm_in, norm_state, o, first_row, slots, heads, dim, vdim, write_state, n_slots, vec_qk, vec_v); \
   } while (0)
 #define FMS_LAUNCH_T(NP, VP, PARTS) FMS_LAUNCH_G(NP, VP, PARTS, true)
 #define FMS_LAUNCH_F(NP, VP, PARTS) FMS_LAUNCH_G(NP, VP, PARTS, false)

@@ -72,7 +72,7 @@ _SIGNATURES = {
     "fms_sigmoid_gate": [_P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _P],
     "fms_normed_add_norm": [_P, _P, _I, _P, _F, _I, _P, _F, _P, _I, _P, _I, _I, _I, _P],
     "fms_linear_prepare": [_P, _I, _I, _P, _I, _I, _I, _F, _I, _P],
-    "fms_decay_scan": [_P, _P, _I, _I, _P, _F, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+    "fms_decay_scan": [_P, _P, _I, _I, _P, _F, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "fms_attention_prefill_sink": [_P, _P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P, _P,
                                    _P],
     "fms_attention_decode_sink": [_P, _P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _F, _I, _I, _I, _L,
@@ -782,9 +782,10 @@ def decay_scan(proj: torch.Tensor, state: torch.Tensor, batch, heads: int, dim: 
           float(q_scale), int(activation), _stream())
     o = torch.empty((n, heads * vdim), dtype=torch.float32, device=proj.device)
     gates = torch.empty((n, heads, 3), dtype=torch.float32, device=proj.device) if gated else None
+    norm_in = torch.empty((batch.n_seqs, heads, dim), dtype=torch.float32, device=proj.device) if gated else None
     gate_ptr = _ptr(proj) + gate_offset * proj.element_size() if gated else None
     _call("state_scan", "fms_decay_scan", _ptr(qkv), gate_ptr, _code(proj.dtype), proj.shape[1], _ptr(gate_bias),
-          float(gate_cap), _ptr(gates), _ptr(decay), _ptr(state), _ptr(norm_state), _ptr(o), _ptr(batch.first_row),
+          float(gate_cap), _ptr(gates), _ptr(norm_in), _ptr(decay), _ptr(state), _ptr(norm_state), _ptr(o), _ptr(batch.first_row),
           _ptr(batch.slots), n, batch.n_seqs, heads, dim, vdim, 1 if writes_state else 0, state.shape[0], _stream())
     global launches
     launches += 1 if gated else 0  # the kernel that walks the gates

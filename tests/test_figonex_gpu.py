@@ -290,13 +290,18 @@ def test_matrix_memory_under_exponential_gates_alone(dtype, shape):
     caps that cut the logits and caps that do not."""
     heads, dim, vdim = shape
     dt, dim_in, n = DTYPES[dtype], 40, 331
-    for case, (cap, i_bias, f_bias) in enumerate(((15.0, 7.0, 5.0), (2.5, -1.0, 1.0), (8.0, -6.0, 3.0))):
+    # the norm that follows divides a head's values by their size, so the read-out's denominator shows only where eps
+    # counts beside them: the second and third case have an eps of the values' own size and above
+    for case, (cap, i_bias, f_bias, eps) in enumerate(((15.0, 7.0, 5.0, 1e-5), (2.5, -1.0, 1.0, 0.5), (8.0, -6.0, 3.0, 8.0))):
         m = fm.mlstm(heads, dim, vdim, cap, None)["mixer"]
         g = torch.Generator().manual_seed(sum(shape) + case)
         w = memory_tensors(g, dim_in, m, True, i_bias=i_bias, f_bias=f_bias)
-        mixer = memory_mixer(m, dim_in, w, 1e-5, dt)
+        mixer = memory_mixer(m, dim_in, w, eps, dt)
         x = torch.randn(n, dim_in, generator=g).to(dt)
-        want = pf.mlstm(x.double(), m, 1e-5, {k: v.double() for k, v in w.items()}, "")
+        d = {k: v.double() for k, v in w.items()}
+        want = pf.mlstm(x.double(), m, eps, d, "")
+        if case:  # the oracle itself says that the denominators show: with no eps the result is another
+            assert (want - pf.mlstm(x.double(), m, 1e-9, d, "")).abs().max() > 0.15 * want.abs().max()
         # whole; portions of one, two, fifteen, sixteen, seventeen rows (the scans bring sixteen rows at a time) and
         # more; a prompt and then row by row
         for cuts in ([n], [1, 2, 15, 16, 17, 1, 33, 246], [250] + [1] * 81):
@@ -336,10 +341,11 @@ def test_memories_that_keep_the_first_tokens_for_a_thousand_steps():
             w["f"] = w["f"] * 0.1
         d = {k: v.double() for k, v in w.items()}
         plain = pf.mlstm if gated else pf.lightning
-        want = plain(x.double(), m, 1e-5, d, "")
-        late = plain(x.double()[200:], m, 1e-5, d, "")
+        eps = 0.3 if gated else 1e-5  # with the gates: large enough for the read-out's denominator to show
+        want = plain(x.double(), m, eps, d, "")
+        late = plain(x.double()[200:], m, eps, d, "")
         assert (want[1000:] - late[800:]).abs().max() > 0.1 * want.abs().max()
-        mixer = memory_mixer(m, dim_in, w, 1e-5, torch.float32)
+        mixer = memory_mixer(m, dim_in, w, eps, torch.float32)
         for cuts in ([n], [1000] + [1] * 100, [7] * 100 + [400]):
             close(step_through(mixer, x.cuda(), cuts, torch.float32), want, "fp32", loose=3.0)
 
