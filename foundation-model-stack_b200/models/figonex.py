@@ -52,8 +52,8 @@ LAYER_TYPES = ("mlstm", "attention", "lightning")
 
 @dataclasses.dataclass
 class FigonexConfig(ModelConfig):
-    vocab: int = 512
-    width: int = 256
+    vocab: int = 1024
+    width: int = 128
     norm_eps: float = 1e-6
     embedding_scale: float = 1.0
     layers: List[Dict[str, Any]] = dataclasses.field(default_factory=list)

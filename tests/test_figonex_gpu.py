@@ -279,7 +279,7 @@ def memory_mixer(m, dim_in, w, eps, dt):
     return part_with(build_mixer(spec), dict(fused, norm=w["norm"], **{"dense.weight": w["o"]}), dt)
 
 
-MEMORY_SHAPES = [(2, 32, 48), (3, 12, 20), (1, 40, 8), (5, 6, 7), (2, 96, 40), (2, 128, 64), (1, 256, 24), (4, 64, 128)]
+MEMORY_SHAPES = [(2, 24, 56), (3, 12, 20), (1, 40, 8), (5, 6, 7), (2, 96, 40), (2, 128, 64), (1, 256, 24), (4, 64, 128)]
 
 
 @pytest.mark.parametrize("dtype", ["fp32", "bf16"])
@@ -334,7 +334,7 @@ def test_memories_that_keep_the_first_tokens_for_a_thousand_steps():
     g = torch.Generator().manual_seed(9)
     x = torch.randn(n, dim_in, generator=g)
     x[:200] *= 3.0
-    for m in (fm.lightning(3, 16, 24, (1.0, 0.999, 0.5), None)["mixer"], fm.mlstm(2, 16, 24, 12.0, None)["mixer"]):
+    for m in (fm.lightning(3, 16, 24, (1.0, 0.999, 0.5), None)["mixer"], fm.mlstm(2, 16, 24, 9.0, None)["mixer"]):
         gated = "gate_cap" in m
         w = memory_tensors(g, dim_in, m, gated, i_bias=-1.0, f_bias=9.0)
         if gated:
