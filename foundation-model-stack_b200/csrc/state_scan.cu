@@ -568,9 +568,10 @@ __global__ void exp_gates_kernel(const T* gate_raw, int stride, const float* bia
     }
     float before = 0.f, after = 0.f;
     const int cn = min(32, hi - base);
-    for (int j = 0; j < cn; ++j) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {  // unrolled: the shuffles are issued ahead and only m waits for the step before
       const float ij = __shfl_sync(0xffffffffu, gi, j), fj = __shfl_sync(0xffffffffu, gf, j);
-      const float next = fmaxf(fj + m, ij);
+      const float next = j < cn ? fmaxf(fj + m, ij) : m;
       if (lane == j) {
         before = m;
         after = next;
