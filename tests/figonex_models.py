@@ -47,6 +47,7 @@ _P_ATT = attention(4, 1, 24, 6, 50.0, 4.0, 0.2, dense(40))
 _P_MEM = mlstm(3, 12, 20, 8.0, dense(40))
 _P_LIN = lightning(2, 12, 20, (0.5, 0.995), dense(40))
 _S_ATT = attention(8, 2, 128, 64, 1000.0, None, 0.09, dense(72))
+_W_ATT = attention(8, 2, 128, 128, 10000.0, None, 0.088, dense(1408))
 
 CONFIGS = {
     # attention first; one key head; a fourth of the head rotated with scaled frequencies; values wider than keys in the
@@ -65,6 +66,10 @@ CONFIGS = {
     # columns), the second attention layer with the first one's weights
     "s": config(101, 64, 2.0, [_S_ATT, mlstm(2, 96, 40, 10.0, dense(72)), lightning(2, 128, 64, (0.98, 0.9), dense(72)),
                                dict(_S_ATT, weights_of=0)]),
+    # a width at which the products of a prompt run on the tensor-core kernels in bfloat16: memories of 128 x 128 and
+    # 128 x 64 (sixteen state rows a thread), eight heads of 128 over two, a feed-forward of 1,408
+    "w": config(2000, 512, 8.0, [mlstm(4, 128, 128, 15.0, dense(1408)), _W_ATT,
+                                 lightning(4, 128, 64, (0.9, 0.99, 0.999, 0.6), dense(1408)), dict(_W_ATT, weights_of=1)]),
 }
 
 

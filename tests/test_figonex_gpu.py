@@ -480,6 +480,24 @@ def test_prompts_cut_into_portions(folders, oracles, which, dtype):
     engine.check()
 
 
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+def test_a_wider_model_whole_in_portions_and_decoding(folders, oracles, dtype):
+    """Width 512 with heads and memories of 128: the kernels that larger models run (tensor-core products and
+    attention of a prompt in bfloat16, sixteen state rows a thread in the scans)."""
+    which = "w"
+    engine = model_of(folders, which, dtype).new_engine(max_tokens=1024, sampling=False)
+    ids = fm.prompt(fm.CONFIGS[which], 300, 43)
+    for cuts in ([300], [180, 2, 118], [258] + [1] * 42):
+        (slot,) = engine.begin(1)
+        got, at = [], 0
+        for n in cuts:
+            got.append(engine.step([slot], [ids[at:at + n]], [list(range(n))]))
+            at += n
+        engine.release([slot])
+        close_logits(torch.cat(got), oracles[K(which, dtype)], ids, dtype)
+    engine.check()
+
+
 @pytest.mark.parametrize("which,dtype", [("p", "fp32"), ("q", "fp32"), ("r", "fp32"), ("s", "fp32"), ("q", "bf16"), ("s", "bf16")])
 def test_unequal_batches_freed_slots_and_poisoned_blocks(folders, oracles, which, dtype):
     """Requests of unequal lengths start together and go on one token at a time while the shorter ones end; then
