@@ -60,7 +60,25 @@ struct AttnArgs {
   // [nheads] float32 or null.  A sink is a term exp(sink[head]) in the softmax's denominator that belongs to no key:
   // it has no value, is not multiplied by the scale, and counts once however the keys are cut into tiles or splits.
   const float* sink;
+  // chunk > 0 (and window == 0): the sequence's positions are cut into runs of `chunk`, counted from position 0, and a
+  // query sees the keys of its own run only.  softcap > 0: a score is softcap * tanh(score / softcap) after the scale.
+  int chunk;
+  float softcap;
 };
+
+// The first position that the query at `pos` sees (its last is pos).  It never decreases as pos grows, so a tile of
+// queries sees nothing before first_visible(its first query) and everything from first_visible(its last) on.
+__device__ __forceinline__ int first_visible(const AttnArgs& a, int pos) {
+  if (a.window > 0) return max(0, pos - a.window + 1);
+  if (a.chunk > 0) return pos - pos % a.chunk;
+  return 0;
+}
+
+// For kernels that fold the scale into the exponent: the raw dot product r replaced by r' with
+// r' * scale = softcap * tanh(r * scale / softcap).
+__device__ __forceinline__ float capped_raw(const AttnArgs& a, float raw) {
+  return tanhf(raw * (a.scale / a.softcap)) * (a.softcap / a.scale);
+}
 
 // The cache block that holds key block kb of the sequence in `slot`; negative: none (a block given back behind a
 // window, or, in the bounds-checked build, an index outside the table or the cache, which is recorded).
@@ -106,8 +124,9 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(AttnArgs a, const int
   const int p_last = p_first + rows_here - 1;
   const int my_pos = p_first + r;
   const bool row_ok = r < rows_here;
-  const int kb_lo = a.window > 0 ? max(0, p_first - a.window + 1) / BLK : 0;
+  const int kb_lo = first_visible(a, p_first) / BLK;
   const int kb_hi = p_last / BLK;
+  const int my_first = first_visible(a, my_pos);
 
   float m = -INFINITY, l = 0.f;
   float acc[HD / 8];
@@ -147,8 +166,8 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(AttnArgs a, const int
       const float* kr = ks + key * (HD + 1);
 #pragma unroll 8
       for (int d = 0; d < HD; ++d) dot = fmaf(qr[d], kr[d], dot);
-      const bool visible = row_ok && kpos <= my_pos && (a.window <= 0 || kpos > my_pos - a.window);
-      s[i] = visible ? dot * a.scale : -INFINITY;
+      const bool visible = row_ok && kpos <= my_pos && kpos >= my_first;
+      s[i] = visible ? (a.softcap > 0.f ? a.softcap * tanhf(dot * a.scale / a.softcap) : dot * a.scale) : -INFINITY;
       tile_max = fmaxf(tile_max, s[i]);
     }
     tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 1));
@@ -217,7 +236,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, float* __r
   const int ng = min(GC, group - g0);   // heads handled here
   const int len = a.len_after[seq];
   const int pos = len - 1;              // the query's position
-  const int kstart = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+  const int kstart = first_visible(a, pos);
   const int k_lo = max(kstart, split * SPLIT), k_hi = min(len, (split + 1) * SPLIT);
   if (k_lo >= k_hi) return;
   const int slot = a.slots[seq];
@@ -267,7 +286,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a, float* __r
 #pragma unroll
       for (int g = 0; g < GC; ++g) {
         const float other = __shfl_xor_sync(0xffffffffu, dot[g], 1);
-        if (half == 0) ss[g][key_of] = valid ? dot[g] + other : -INFINITY;
+        const float sc = dot[g] + other;  // the scale is in the queries
+        if (half == 0) ss[g][key_of] = valid ? (a.softcap > 0.f ? a.softcap * tanhf(sc / a.softcap) : sc) : -INFINITY;
       }
     }
     __syncthreads();
@@ -372,7 +392,7 @@ __global__ void attn_combine_kernel(AttnArgs a, const float* __restrict__ part_o
 #pragma unroll
   for (int i = 0; i < COMBINE_EARLY; ++i) early[i] = i < n_splits ? po[(size_t)i * HD + d] : 0.f;
   const int pos = len - 1;
-  const int kstart = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+  const int kstart = first_visible(a, pos);
   int s_lo = kstart / SPLIT, s_hi = pos / SPLIT;
   if (s_hi >= n_splits) {
     // a sequence longer than the launch's splits cover (the caller's n_splits is too small): nothing beyond the
@@ -424,6 +444,13 @@ int check_args(const char* what, int nheads, int kvheads, int head_dim, int bloc
   if (head_dim != HD) return fms_fail("%s: this library is built for head size %d, not %d", what, HD, head_dim);
   if (block_tokens != BLK) return fms_fail("%s: cache blocks of %d tokens, %d expected", what, block_tokens, BLK);
   if (nheads <= 0 || kvheads <= 0 || nheads % kvheads) return fms_fail("%s: %d heads over %d kv heads", what, nheads, kvheads);
+  return 0;
+}
+
+int check_mask(const char* what, int window, int chunk, float softcap) {
+  if (window < 0 || chunk < 0 || (window > 0 && chunk > 0))
+    return fms_fail("%s: window %d, chunk %d: one of them at most, neither negative", what, window, chunk);
+  if (softcap < 0.f) return fms_fail("%s: a cap of %g on the scores", what, (double)softcap);
   return 0;
 }
 
@@ -555,11 +582,13 @@ static int attention_prefill(const void* q, void* out, int dtype, const void* ke
                              const int* table, int table_stride, int block_tokens, const int* slots,
                              const int* first_row, const int* len_after, const int* tiles, int n_tiles,
                              int nheads, int kvheads, int head_dim, float scale, int window, int pool_blocks,
-                             int table_rows, int* error_flag, const float* sink, cudaStream_t stream) {
+                             int table_rows, int* error_flag, const float* sink, cudaStream_t stream, int chunk = 0,
+                             float softcap = 0.f) {
   if (n_tiles <= 0) return 0;
   if (check_args("attention_prefill", nheads, kvheads, head_dim, block_tokens)) return 1;
+  if (check_mask("attention_prefill", window, chunk, softcap)) return 1;
   AttnArgs a{q, out, keys, values, table, table_stride, slots, first_row, len_after, nheads, kvheads, scale, window,
-             table_rows, pool_blocks, sink};
+             table_rows, pool_blocks, sink, chunk, softcap};
   if (nheads > 65535) return fms_fail("attention_prefill: %d heads", nheads);
   if (!(scale > 0.f)) return fms_fail("attention_prefill: the scale of the scores is %g; it must be positive", (double)scale);
 #if FMS_ATTENTION_TC
@@ -630,6 +659,19 @@ FMS_API int fms_attention_prefill_sink(const void* q, void* out, int dtype, cons
                            sink, stream);
 }
 
+// The same with, each of them optional, a sink per head (null: none), keys seen in runs of `chunk` positions (0: all
+// keys, or the window's) and capped scores (softcap 0: none).
+FMS_API int fms_attention_prefill_masked(const void* q, void* out, int dtype, const void* keys, const void* values,
+                                         const int* table, int table_stride, int block_tokens, const int* slots,
+                                         const int* first_row, const int* len_after, const int* tiles, int n_tiles,
+                                         int nheads, int kvheads, int head_dim, float scale, int window, int pool_blocks,
+                                         int table_rows, int* error_flag, const float* sink, int chunk, float softcap,
+                                         cudaStream_t stream) {
+  return attention_prefill(q, out, dtype, keys, values, table, table_stride, block_tokens, slots, first_row, len_after,
+                           tiles, n_tiles, nheads, kvheads, head_dim, scale, window, pool_blocks, table_rows, error_flag,
+                           sink, stream, chunk, softcap);
+}
+
 // part_o: float [seqs, nheads, n_splits, HD]; part_ml: float [seqs, nheads, n_splits, 2]; both scratch.
 // pool_blocks: blocks in the cache (bounds the early L2 hints and the streaming kernel's tensor maps; 0 turns both
 // off).  table_rows: slots the table has rows for (looked at by the bounds-checked build only; 0: not known).  total_len: cached tokens of all sequences together as far as the host knows (0: unknown), by which the
@@ -663,6 +705,23 @@ FMS_API int fms_attention_decode_sink(const void* q, void* out, int dtype, const
   if (!(scale > 0.f)) return fms_fail("attention_decode: the scale of the scores is %g; it must be positive", (double)scale);
   AttnArgs a{q, out, keys, values, table, table_stride, slots, first_row, len_after, nheads, kvheads, scale, window,
              table_rows, pool_blocks, sink};
+  return launch_decode("attention_decode", a, dtype, n_seqs, n_splits, part_o, part_ml, pool_blocks, total_len, work_counter, error_flag, stream);
+}
+
+// The same with, each of them optional, a sink per head (null: none), keys seen in runs of `chunk` positions (0: all
+// keys, or the window's) and capped scores (softcap 0: none).
+FMS_API int fms_attention_decode_masked(const void* q, void* out, int dtype, const void* keys, const void* values,
+                                        const int* table, int table_stride, int block_tokens, const int* slots,
+                                        const int* first_row, const int* len_after, int n_seqs, int n_splits, float* part_o,
+                                        float* part_ml, int nheads, int kvheads, int head_dim, float scale, int window,
+                                        int pool_blocks, int table_rows, long total_len, int* work_counter, int* error_flag,
+                                        const float* sink, int chunk, float softcap, cudaStream_t stream) {
+  if (n_seqs <= 0) return 0;
+  if (check_args("attention_decode", nheads, kvheads, head_dim, block_tokens)) return 1;
+  if (check_mask("attention_decode", window, chunk, softcap)) return 1;
+  if (!(scale > 0.f)) return fms_fail("attention_decode: the scale of the scores is %g; it must be positive", (double)scale);
+  AttnArgs a{q, out, keys, values, table, table_stride, slots, first_row, len_after, nheads, kvheads, scale, window,
+             table_rows, pool_blocks, sink, chunk, softcap};
   return launch_decode("attention_decode", a, dtype, n_seqs, n_splits, part_o, part_ml, pool_blocks, total_len, work_counter, error_flag, stream);
 }
 

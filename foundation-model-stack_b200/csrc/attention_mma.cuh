@@ -129,7 +129,7 @@ __global__ void __launch_bounds__(NW * 32, WK == 32 ? 16 / NW : 12 / NW)
   // (Loads that bypass L1, so that no stale line is found again after the wait.)
   if (pool_blocks > 0 && lane == 0) {
     const int len0 = __ldcg(a.len_after + seq), slot0 = __ldcg(a.slots + seq);
-    const int start0 = a.window > 0 ? max(0, len0 - a.window) : 0;
+    const int start0 = len0 > 0 ? first_visible(a, len0 - 1) : 0;
     const int lo0 = max(start0, split * SPLIT), hi0 = min(len0, (split + 1) * SPLIT);
     if (slot0 >= 0) {
       for (int piece = lo0 / WK + warp; piece * WK < hi0 && piece * WK / BLK < a.table_stride; piece += NW) {
@@ -149,7 +149,7 @@ __global__ void __launch_bounds__(NW * 32, WK == 32 ? 16 / NW : 12 / NW)
   const int slot = a.slots[seq];
   const int first_row = a.first_row[seq];
   const int pos = len - 1;
-  const int kstart = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+  const int kstart = first_visible(a, pos);
   const int k_lo = max(kstart, split * SPLIT), k_hi = min(len, (split + 1) * SPLIT);
   if (k_lo >= k_hi) return;
   const __nv_bfloat16* q = (const __nv_bfloat16*)a.q + (size_t)first_row * a.nheads * HD +
@@ -247,6 +247,12 @@ __global__ void __launch_bounds__(NW * 32, WK == 32 ? 16 / NW : 12 / NW)
       }
     }
     // raw scores; the scale (positive) goes into the exponent's multiply-add
+    if (a.softcap > 0.f) {
+#pragma unroll
+      for (int t = 0; t < WT; ++t)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) st[t][e] = capped_raw(a, st[t][e]);
+    }
     if (!whole) {
 #pragma unroll
       for (int t = 0; t < WT; ++t)
@@ -409,7 +415,7 @@ __global__ void __launch_bounds__(PF_WARPS * 32, HD <= 128 ? 3 : 1) attn_prefill
   const __nv_bfloat16* vc = (const __nv_bfloat16*)a.values;
 
   // the two rows of this lane: tile row -> (position index, head index)
-  int row_pos[2];
+  int row_pos[2], row_first[2];
   bool row_ok[2];
   const __nv_bfloat16* qrow[2];
   __nv_bfloat16* orow[2];
@@ -419,6 +425,7 @@ __global__ void __launch_bounds__(PF_WARPS * 32, HD <= 128 ? 3 : 1) attn_prefill
     const int pi = r / gh, gi = r - pi * gh;
     row_ok[h] = pi < pos_here && gi < ng;
     row_pos[h] = p_first + pi;
+    row_first[h] = first_visible(a, row_pos[h]);
     const size_t at = ((size_t)(row_begin + r0 + (row_ok[h] ? pi : 0)) * a.nheads + kvh * group + g0 + (row_ok[h] ? gi : 0)) * HD;
     qrow[h] = q + at;
     orow[h] = (__nv_bfloat16*)a.out + at;
@@ -439,7 +446,7 @@ __global__ void __launch_bounds__(PF_WARPS * 32, HD <= 128 ? 3 : 1) attn_prefill
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};  // running maximum in units of log2, and sum
   const float scale2 = a.scale * LOG2E;  // scores are kept times log2(e): exp(x) = exp2(x log2 e)
 
-  const int kb_lo = a.window > 0 ? max(0, p_first - a.window + 1) / BLK : 0;
+  const int kb_lo = first_visible(a, p_first) / BLK;
   const int kb_hi = p_last / BLK;
   const int nblocks = kb_hi - kb_lo + 1;
   constexpr int STAGE = 2 * BLK * ROWB;
@@ -471,7 +478,13 @@ __global__ void __launch_bounds__(PF_WARPS * 32, HD <= 128 ? 3 : 1) attn_prefill
     float s[8][4];
     scores_16x64(s, qf, kbuf, lane);
     // a block that every row of the tile sees whole needs no mask
-    const bool whole = kb * BLK + BLK - 1 <= p_first && (a.window <= 0 || kb * BLK > p_last - a.window);
+    const bool whole = kb * BLK + BLK - 1 <= p_first && kb * BLK >= first_visible(a, p_last);
+    if (a.softcap > 0.f) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[j][e] = capped_raw(a, s[j][e]);
+    }
     float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int j = 0; j < 8; ++j)
@@ -479,7 +492,7 @@ __global__ void __launch_bounds__(PF_WARPS * 32, HD <= 128 ? 3 : 1) attn_prefill
       for (int e = 0; e < 4; ++e) {
         const int h = e >> 1;
         const int kpos = kb * BLK + 8 * j + 2 * c + (e & 1);
-        const bool visible = whole || (kpos <= row_pos[h] && (a.window <= 0 || kpos > row_pos[h] - a.window));
+        const bool visible = whole || (kpos <= row_pos[h] && kpos >= row_first[h]);
         s[j][e] = (visible && row_ok[h]) ? s[j][e] * scale2 : -INFINITY;
         tile_max[h] = fmaxf(tile_max[h], s[j][e]);
       }

@@ -90,7 +90,7 @@ __global__ void __launch_bounds__((SR_WARPS + 1) * 32, 1)
         y = (int)(rest % ny);
         split = (int)(rest / ny);
         const int len = a.len_after[seq];
-        const int kstart = a.window > 0 ? max(0, len - a.window) : 0;
+        const int kstart = len > 0 ? first_visible(a, len - 1) : 0;
         k_lo = max(kstart, split * SPLIT);
         k_hi = min(len, (split + 1) * SPLIT);
         if (k_lo >= k_hi) continue;
@@ -185,6 +185,12 @@ __global__ void __launch_bounds__((SR_WARPS + 1) * 32, 1)
           mma16816(st[t], ka, qf[ks][0], qf[ks][1]);
         }
       }
+    }
+    if (a.softcap > 0.f) {
+#pragma unroll
+      for (int t = 0; t < 4; ++t)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) st[t][e] = capped_raw(a, st[t][e]);
     }
     if (!whole) {
 #pragma unroll

@@ -80,7 +80,7 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
   const int slot = a.slots[seq];
   const int pos_here = min(pp, n_new - r0);
   const int p_first = len_before + r0, p_last = p_first + pos_here - 1;
-  const int kb_lo = a.window > 0 ? max(0, p_first - a.window + 1) / BLK : 0;
+  const int kb_lo = first_visible(a, p_first) / BLK;
   const int kb_hi = p_last / BLK;
   const int nblocks = kb_hi - kb_lo + 1;
 
@@ -172,6 +172,7 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
     const int pi = r / gh, gi = r - pi * gh;
     const bool row_ok = pi < pos_here && gi < ng;
     const int my_pos = p_first + pi;
+    const int my_first = first_visible(a, my_pos);
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     // the query tile: row r, 16-byte piece c of 64-value chunk t at t * 16 KB + r * 128 + ((c ^ (r & 7)) << 4)
     {
@@ -198,12 +199,16 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
       tmem_load_2x32(tmem_s + (i & 1) * BLK + lane_base, tmem_s + (i & 1) * BLK + lane_base + 32, sc, sc + 32);
       // raw scores; the scale (positive) goes into the exponent's multiply-add.  A block that every row of the tile
       // sees whole needs no mask; rows without a query hold zeros there and are never stored.
-      const bool whole = kb * BLK + BLK - 1 <= p_first && (a.window <= 0 || kb * BLK > p_last - a.window);
+      const bool whole = kb * BLK + BLK - 1 <= p_first && kb * BLK >= first_visible(a, p_last);
+      if (a.softcap > 0.f) {
+#pragma unroll
+        for (int j = 0; j < BLK; ++j) sc[j] = capped_raw(a, sc[j]);
+      }
       if (!whole) {
 #pragma unroll
         for (int j = 0; j < BLK; ++j) {
           const int kpos = kb * BLK + j;
-          const bool visible = row_ok && kpos <= my_pos && (a.window <= 0 || kpos > my_pos - a.window);
+          const bool visible = row_ok && kpos <= my_pos && kpos >= my_first;
           sc[j] = visible ? sc[j] : -INFINITY;
         }
       }

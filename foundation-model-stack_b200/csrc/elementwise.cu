@@ -875,12 +875,129 @@ FMS_API int fms_cast_rows(const float* x, void* out, int dtype, long n, cudaStre
 }
 
 // ---------------------------------------------------------------------------------------------------
+// norm in groups, for layers whose sublayers run side by side on the same stream:
+//   x = residual[r] + s0 d0[r] + s1 d1[r] + s2 d2[r] + s3 d3[r]        (the parts that are given; float32)
+//   residual[r] = x                                                     (not with `rows`: then row rows[i] is read)
+//   the row in `groups` equal consecutive runs, each run y = x / sqrt(mean(x^2 over the run) + eps)
+//   out1 = y * gain1, out2 = y * gain2 (where asked for): two norms of the same stream share their statistics
+// A warp per (row, run), or a block per (row, run) for runs of 1,024 values and more; four values a thread where the
+// run's size and the addresses allow.  The sums of a run are taken in the same order whatever else the step holds.
+// ---------------------------------------------------------------------------------------------------
+struct NormParts {
+  const void* d[4];
+  float s[4];
+};
+
+template <typename T, int VEC, bool WHOLE_BLOCK>
+__global__ void parts_group_rmsnorm_kernel(float* residual, NormParts parts, const float* gain1, const float* gain2, float eps,
+                                           int groups, T* out1, T* out2, const int* rows, int n_rows, int dim, int n_res) {
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane_n = WHOLE_BLOCK ? blockDim.x : 32;
+  const int lane = WHOLE_BLOCK ? threadIdx.x : (threadIdx.x & 31);
+  const long item = WHOLE_BLOCK ? (long)blockIdx.x : (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= (long)n_rows * groups) return;  // a warp (or the block) as a whole
+  const int r = (int)(item / groups), grp = (int)(item - (long)r * groups);
+  const int gs = dim / groups;
+  int src = r;
+  if (rows) {
+    src = __ldcg(rows + r);
+    if (!FMS_IN(src, n_res)) return;
+  }
+  const size_t at = (size_t)src * dim + (size_t)grp * gs, out_at = (size_t)r * dim + (size_t)grp * gs;
+  float* res = residual + at;
+  const bool write_res = rows == nullptr;
+  auto summed = [&](int e, float (&x)[VEC]) {
+    if constexpr (VEC == 4) {
+      ldv4(res + e, x);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        if (parts.d[k]) {
+          float v[4];
+          ldv4((const T*)parts.d[k] + at + e, v);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) x[j] = fmaf(parts.s[k], v[j], x[j]);
+        }
+      }
+    } else {
+      x[0] = res[e];
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (parts.d[k]) x[0] = fmaf(parts.s[k], to_f32(((const T*)parts.d[k])[at + e]), x[0]);
+    }
+  };
+  float ss = 0.f;
+  for (int e = lane * VEC; e < gs; e += lane_n * VEC) {
+    float x[VEC];
+    summed(e, x);
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) ss += x[j] * x[j];
+    if (write_res) {
+      if constexpr (VEC == 4) stv4(res + e, x);
+      else res[e] = x[0];
+    }
+  }
+  const float total = WHOLE_BLOCK ? block_sum(ss, scratch) : warp_sum(ss);
+  const float inv = 1.f / sqrtf(total / (float)gs + eps);
+  for (int e = lane * VEC; e < gs; e += lane_n * VEC) {
+    float x[VEC];
+    if (write_res) {  // this thread's own earlier store
+      if constexpr (VEC == 4) ldv4(res + e, x);
+      else x[0] = res[e];
+    } else {
+      summed(e, x);
+    }
+    float y[VEC];
+    if (out1) {
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) y[j] = x[j] * inv * gain1[grp * gs + e + j];
+      if constexpr (VEC == 4) stv4(out1 + out_at + e, y);
+      else out1[out_at + e] = from_f32<T>(y[0]);
+    }
+    if (out2) {
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) y[j] = x[j] * inv * gain2[grp * gs + e + j];
+      if constexpr (VEC == 4) stv4(out2 + out_at + e, y);
+      else out2[out_at + e] = from_f32<T>(y[0]);
+    }
+  }
+}
+
+FMS_API int fms_parts_group_rmsnorm(float* residual, const void* d0, float s0, const void* d1, float s1, const void* d2,
+                                    float s2, const void* d3, float s3, const float* gain1, const float* gain2, float eps,
+                                    int groups, void* out1, void* out2, int dtype, const int* rows, int n_rows, int dim,
+                                    int n_res, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (dim <= 0 || groups <= 0 || dim % groups) return fms_fail("parts_group_rmsnorm: a row of %d values in %d runs", dim, groups);
+  if ((out1 && !gain1) || (out2 && !gain2)) return fms_fail("parts_group_rmsnorm: an output without its gain");
+  NormParts parts{{d0, d1, d2, d3}, {s0, s1, s2, s3}};
+  const int gs = dim / groups;
+  const size_t item = dtype == FMS_BF16 ? 2 : 4;
+  bool four = gs % 4 == 0 && (uintptr_t)residual % 16 == 0 && (uintptr_t)out1 % (4 * item) == 0 && (uintptr_t)out2 % (4 * item) == 0;
+  for (int k = 0; k < 4; ++k) four = four && (uintptr_t)parts.d[k] % (4 * item) == 0;
+  const long items = (long)n_rows * groups;
+  const bool whole = gs >= 1024;
+  const dim3 grid((unsigned)(whole ? items : (items + 3) / 4)), block(whole ? (gs >= 4096 ? 512 : 256) : 128);
+#define FMS_GROUP_NORM(VEC, WHOLE)                                                                                      \
+  FMS_DISPATCH_DTYPE(dtype, T, fms_launch(parts_group_rmsnorm_kernel<T, VEC, WHOLE>, grid, block, 0, stream, residual, parts, \
+                                          gain1, gain2, eps, groups, (T*)out1, (T*)out2, rows, n_rows, dim, n_res))
+  if (four && whole) FMS_GROUP_NORM(4, true);
+  else if (four) FMS_GROUP_NORM(4, false);
+  else if (whole) FMS_GROUP_NORM(1, true);
+  else FMS_GROUP_NORM(1, false);
+#undef FMS_GROUP_NORM
+  return fms_launch_status("parts_group_rmsnorm");
+}
+
+// ---------------------------------------------------------------------------------------------------
 // queries, keys and values of a step on their way into attention, for heads whose first `rot` values are rotated,
 // whose queries and keys may be divided by their root mean square afterwards, and whose value size may differ from
 // the key size:
 //   proj[t] = [q: nheads x dim | k: kvheads x dim | v: kvheads x vdim | ...]   (row stride `stride`)
 //   q, k: pairs (2i, 2i+1), i < rot / 2, rotated by position * inv_freq[i]; the other values pass
-//         (`halves`: the pairs are (i, i + rot / 2) instead)
+//         (`halves`: the pairs are (i, i + rot / 2) instead; `rot_mult` multiplies the sines and cosines, 1 for a
+//         plain rotation: stretched frequencies come with such a constant)
 //   q, k: x / sqrt(mean(x^2) + eps) over the head's dim values, where qk_norm is set (no gain)
 //         (`norm_first`: the norm comes before the rotation, times q_gain / k_gain [dim] where those are given)
 //   `v_from_k`: there are no value columns; the value is the key as projected, before norm and rotation
@@ -892,7 +1009,7 @@ constexpr int PREP_MAX_PAIRS = 256;
 
 template <typename T>
 __global__ void qk_prepare_store_kernel(const T* proj, int stride, T* q_out, const float* inv_freq, int rot,
-                                        int qk_norm, float eps, const float* q_gain, const float* k_gain, int norm_first,
+                                        float rot_mult, int qk_norm, float eps, const float* q_gain, const float* k_gain, int norm_first,
                                         int halves, int v_from_k, const int* positions, const int* position_ids,
                                         const int* token_seq, const int* slots, T* k_cache, T* v_cache, const int* table,
                                         int table_stride, int block_tokens, int nheads, int kvheads, int dim, int vdim,
@@ -907,7 +1024,7 @@ __global__ void qk_prepare_store_kernel(const T* proj, int stride, T* q_out, con
   for (int i = threadIdx.x; i < rot / 2; i += blockDim.x) {
     float s, c;
     sincosf((float)pid * inv_freq[i], &s, &c);
-    sc[i] = make_float2(s, c);
+    sc[i] = make_float2(s * rot_mult, c * rot_mult);
   }
   __syncthreads();
   const int lane = threadIdx.x & 31;
@@ -988,7 +1105,7 @@ __global__ void qk_prepare_store_kernel(const T* proj, int stride, T* q_out, con
 }
 
 FMS_API int fms_qk_prepare_store(const void* proj, int dtype, int stride, void* q_out, const float* inv_freq, int rot,
-                                 int qk_norm, float eps, const float* q_gain, const float* k_gain, int norm_first,
+                                 float rot_mult, int qk_norm, float eps, const float* q_gain, const float* k_gain, int norm_first,
                                  int halves, int v_from_k, const int* positions, const int* position_ids,
                                  const int* token_seq, const int* slots, void* k_cache, void* v_cache, const int* table,
                                  int table_stride, int block_tokens, int n_tokens, int nheads, int kvheads, int dim,
@@ -1003,7 +1120,7 @@ FMS_API int fms_qk_prepare_store(const void* proj, int dtype, int stride, void* 
   FMS_DISPATCH_DTYPE(dtype, T,
                      fms_launch(qk_prepare_store_kernel<T>, dim3(n_tokens, (nheads + 2 * kvheads + 3) / 4), dim3(128), 0, stream,
                                 (const T*)proj, stride,
-                                (T*)q_out, inv_freq, rot, qk_norm, eps, q_gain, k_gain, norm_first, halves, v_from_k,
+                                (T*)q_out, inv_freq, rot, rot_mult, qk_norm, eps, q_gain, k_gain, norm_first, halves, v_from_k,
                                 positions, position_ids, token_seq, slots,
                                 (T*)k_cache, (T*)v_cache, table, table_stride, block_tokens, nheads, kvheads, dim, vdim, pad,
                                 write_cache, error_flag, n_seqs, table_rows, pool_blocks));

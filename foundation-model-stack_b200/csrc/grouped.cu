@@ -27,6 +27,15 @@ __device__ __forceinline__ float ld_fresh(const float* p) { return __ldcg(p); }
 namespace {
 constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
 
+// what an ungated product's sums go through: act 2 is the square of relu, anything else nothing
+__device__ __forceinline__ float activated(float v, int act) {
+  if (act == 2) {
+    v = fmaxf(v, 0.f);
+    v *= v;
+  }
+  return v;
+}
+
 __device__ __forceinline__ float glu_clamped(float g, float u, float limit, float alpha) {
   g = fminf(g, limit);
   u = fminf(fmaxf(u, -limit), limit);
@@ -39,7 +48,7 @@ __global__ void __launch_bounds__(256) grouped_gemm_kernel(const T* __restrict__
                                                            const int* __restrict__ tile_first, int groups, int rows,
                                                            int N, int K, long x_row_stride, long x_group_offset,
                                                            long y_row_stride, long y_group_offset, float limit,
-                                                           float alpha) {
+                                                           float alpha, int act) {
   __shared__ float xs[BK][BM + 4];
   __shared__ float ws[GLU ? 2 : 1][BK][BN + 4];
   pdl_launch_dependents();
@@ -115,7 +124,7 @@ __global__ void __launch_bounds__(256) grouped_gemm_kernel(const T* __restrict__
     for (int j = 0; j < TN; ++j) {
       const int gn = n0 + tn + j;
       if (gn >= N) continue;
-      const float v = GLU ? glu_clamped(acc[0][i][j], acc[GLU ? 1 : 0][i][j], limit, alpha) : acc[0][i][j];
+      const float v = GLU ? glu_clamped(acc[0][i][j], acc[GLU ? 1 : 0][i][j], limit, alpha) : activated(acc[0][i][j], act);
       y[(size_t)gm * y_row_stride + gn] = from_f32<T>(v);
     }
   }
@@ -146,7 +155,7 @@ template <typename T, bool GLU>
 __global__ void __launch_bounds__(256) grouped_rows_kernel(const T* x, const T* w, T* y, const int* offsets, int groups,
                                                            int rows, int N, int K, long x_row_stride, long x_group_offset,
                                                            long y_row_stride, long y_group_offset, float limit,
-                                                           float alpha, int vec) {
+                                                           float alpha, int vec, int act) {
   pdl_launch_dependents();
   pdl_wait();
   const int g = blockIdx.y;
@@ -198,7 +207,7 @@ __global__ void __launch_bounds__(256) grouped_rows_kernel(const T* x, const T* 
     for (int i = 0; i < 4; ++i)
       if (i < nr) {
         const float s0 = warp_sum(a0[i]), s1 = GLU ? warp_sum(a1[i]) : 0.f;
-        if (lane == 0) y[(size_t)(r0 + i) * y_row_stride + n] = from_f32<T>(GLU ? glu_clamped(s0, s1, limit, alpha) : s0);
+        if (lane == 0) y[(size_t)(r0 + i) * y_row_stride + n] = from_f32<T>(GLU ? glu_clamped(s0, s1, limit, alpha) : activated(s0, act));
       }
   }
 }
@@ -246,10 +255,12 @@ constexpr int ROUTE_WARPS = 8;
 template <typename T, typename TW>
 __global__ void __launch_bounds__(32 * ROUTE_WARPS) route_kernel(const T* __restrict__ x, const TW* __restrict__ router,
                                                     int* __restrict__ expert, float* __restrict__ weight,
-                                                    int dim, int experts, int top) {
-  extern __shared__ float sm[];  // dim values of x, then `experts` logits
+                                                    int dim, int experts, int top, int mode,
+                                                    const float* __restrict__ correction, float route_scale) {
+  extern __shared__ float sm[];  // dim values of x, then `experts` logits, then (mode 1) `experts` scores
   float* xs = sm;
   float* logit = sm + dim;
+  float* score = logit + experts;
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -271,6 +282,23 @@ __global__ void __launch_bounds__(32 * ROUTE_WARPS) route_kernel(const T* __rest
   }
   __syncthreads();
   if (warp != 0) return;
+  if (mode == 1) {
+    // scores = softmax over all experts; the choice is by score + correction, the weights are the chosen scores over
+    // their sum (+ 1e-20), times route_scale
+    float mx = -INFINITY;
+    for (int e = lane; e < experts; e += 32) mx = fmaxf(mx, logit[e]);
+    mx = warp_max(mx);
+    float den = 0.f;
+    for (int e = lane; e < experts; e += 32) den += expf(logit[e] - mx);
+    den = warp_sum(den);
+    for (int e = lane; e < experts; e += 32) {
+      const float sc = expf(logit[e] - mx) / den;
+      score[e] = sc;
+      logit[e] = sc + (correction ? correction[e] : 0.f);
+    }
+    __syncwarp();
+  }
+  float picked_sum = 0.f;
   for (int k = 0; k < top; ++k) {
     float best = -INFINITY;
     int at = 0x7fffffff;
@@ -293,10 +321,15 @@ __global__ void __launch_bounds__(32 * ROUTE_WARPS) route_kernel(const T* __rest
     if (at >= experts) at = k;  // every logit was NaN or -inf: any expert, so that nothing below reads outside
     if (lane == 0) {
       expert[(size_t)t * top + k] = at;
-      weight[(size_t)t * top + k] = 1.f / (1.f + expf(-best));
+      weight[(size_t)t * top + k] = mode == 1 ? score[at] : 1.f / (1.f + expf(-best));
       logit[at] = -INFINITY;
     }
+    if (mode == 1) picked_sum += score[at];
     __syncwarp();
+  }
+  if (mode == 1 && lane == 0) {
+    const float f = route_scale / (picked_sum + 1e-20f);
+    for (int k = 0; k < top; ++k) weight[(size_t)t * top + k] *= f;
   }
 }
 
@@ -335,7 +368,8 @@ __global__ void __launch_bounds__(128) route_scatter_kernel(const T* __restrict_
                                                             const float* __restrict__ weight,
                                                             const int* __restrict__ offsets, int* __restrict__ placed,
                                                             int* __restrict__ row_of_pair, int* __restrict__ group_of_row,
-                                                            T* __restrict__ xs, int dim, int top, int experts, int n_pairs) {
+                                                            T* __restrict__ xs, int dim, int top, int experts, int n_pairs,
+                                                            int weighted) {
   __shared__ int where;
   pdl_launch_dependents();
   pdl_wait();
@@ -350,26 +384,34 @@ __global__ void __launch_bounds__(128) route_scatter_kernel(const T* __restrict_
   __syncthreads();
   const int row = where;
   if (!FMS_IN(row, n_pairs)) return;
-  const float wgt = ld_fresh(weight + p);
+  const float wgt = weighted ? ld_fresh(weight + p) : 1.f;
   const T* src = x + (size_t)(p / top) * dim;
   T* dst = xs + (size_t)row * dim;
-  for (int d = threadIdx.x; d < dim; d += blockDim.x) dst[d] = from_f32<T>(wgt * to_f32(src[d]));
+  if (weighted)
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) dst[d] = from_f32<T>(wgt * to_f32(src[d]));
+  else
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) dst[d] = src[d];
 }
 
 template <typename T>
 __global__ void __launch_bounds__(256) route_gather_kernel(const T* __restrict__ ys, const int* __restrict__ row_of_pair,
-                                                           T* __restrict__ out, int dim, int top, int n_pairs) {
+                                                           T* __restrict__ out, int dim, int top, int n_pairs,
+                                                           const float* weight) {
   pdl_launch_dependents();
   pdl_wait();
-  extern __shared__ int rows_of_token[];
+  extern __shared__ int rows_of_token[];  // then, as floats, the pairs' weights
+  float* weight_of_token = reinterpret_cast<float*>(rows_of_token + top);
   const int t = blockIdx.x;
-  for (int k = threadIdx.x; k < top; k += blockDim.x) rows_of_token[k] = ld_fresh(row_of_pair + (size_t)t * top + k);
+  for (int k = threadIdx.x; k < top; k += blockDim.x) {
+    rows_of_token[k] = ld_fresh(row_of_pair + (size_t)t * top + k);
+    weight_of_token[k] = weight ? ld_fresh(weight + (size_t)t * top + k) : 1.f;
+  }
   __syncthreads();
   for (int d = threadIdx.x; d < dim; d += blockDim.x) {
     float a = 0.f;
     for (int k = 0; k < top; ++k) {
       const int row = rows_of_token[k];
-      if (FMS_IN(row, n_pairs)) a += to_f32(ys[(size_t)row * dim + d]);
+      if (FMS_IN(row, n_pairs)) a = fmaf(weight_of_token[k], to_f32(ys[(size_t)row * dim + d]), a);
     }
     out[(size_t)t * dim + d] = from_f32<T>(a);
   }
@@ -380,12 +422,15 @@ FMS_API int fms_grouped_tile_rows() { return BM; }
 
 // offsets null: uniform groups of `rows` rows; else ragged groups, `rows` = all rows of x, and tile_first as
 // fms_route leaves it.  few_rows != 0: the kernel that walks each group's rows (a decode step).
+// glu: 0 plain, 1 the gated unit over [gate; up] rows, 2 an ungated product whose sums are squared where positive.
 FMS_API int fms_grouped_linear(const void* x, const void* w, void* y, int dtype, const int* offsets, const int* tile_first,
                                const int* group_of_row, int groups, int rows, int N, int K, long x_row_stride,
                                long x_group_offset, long y_row_stride, long y_group_offset, int glu, float limit,
                                float alpha, int few_rows, cudaStream_t stream) {
   if (rows <= 0 || groups <= 0 || N <= 0) return 0;
   if (K <= 0) return fms_fail("grouped_linear: K %d", K);
+  const int act = glu == 2 ? 2 : 0;
+  glu = glu == 1 ? 1 : 0;
   if (few_rows) {
     if (groups > 65535) return fms_fail("grouped_linear: %d groups are more than the row-by-row kernel takes", groups);
     dim3 grid((N + 7) / 8, groups);
@@ -394,10 +439,10 @@ FMS_API int fms_grouped_linear(const void* x, const void* w, void* y, int dtype,
     FMS_DISPATCH_DTYPE(dtype, T, {
       if (glu)
         fms_launch(grouped_rows_kernel<T, true>, grid, dim3(256), 0, stream, (const T*)x, (const T*)w, (T*)y, offsets, groups,
-                   rows, N, K, x_row_stride, x_group_offset, y_row_stride, y_group_offset, limit, alpha, vec);
+                   rows, N, K, x_row_stride, x_group_offset, y_row_stride, y_group_offset, limit, alpha, vec, act);
       else
         fms_launch(grouped_rows_kernel<T, false>, grid, dim3(256), 0, stream, (const T*)x, (const T*)w, (T*)y, offsets, groups,
-                   rows, N, K, x_row_stride, x_group_offset, y_row_stride, y_group_offset, limit, alpha, vec);
+                   rows, N, K, x_row_stride, x_group_offset, y_row_stride, y_group_offset, limit, alpha, vec, act);
     });
     return fms_launch_status("grouped_linear (few rows)");
   }
@@ -413,10 +458,10 @@ FMS_API int fms_grouped_linear(const void* x, const void* w, void* y, int dtype,
   FMS_DISPATCH_DTYPE(dtype, T, {
     if (glu)
       fms_launch(grouped_gemm_kernel<T, true>, grid, dim3(256), 0, stream, (const T*)x, (const T*)w, (T*)y, offsets,
-                 tile_first, groups, rows, N, K, x_row_stride, x_group_offset, y_row_stride, y_group_offset, limit, alpha);
+                 tile_first, groups, rows, N, K, x_row_stride, x_group_offset, y_row_stride, y_group_offset, limit, alpha, act);
     else
       fms_launch(grouped_gemm_kernel<T, false>, grid, dim3(256), 0, stream, (const T*)x, (const T*)w, (T*)y, offsets,
-                 tile_first, groups, rows, N, K, x_row_stride, x_group_offset, y_row_stride, y_group_offset, limit, alpha);
+                 tile_first, groups, rows, N, K, x_row_stride, x_group_offset, y_row_stride, y_group_offset, limit, alpha, act);
   });
   return fms_launch_status("grouped_linear");
 }
@@ -424,17 +469,21 @@ FMS_API int fms_grouped_linear(const void* x, const void* w, void* y, int dtype,
 // x [n_tokens, dim] in `dtype`, router [experts, dim] in `router_dtype`.  Out: expert, weight [n_tokens, top];
 // offsets, tile_first [experts + 1]; row_of_pair [n_tokens * top]; group_of_row [n_tokens * top]; xs [n_tokens * top, dim].
 // counts [experts] is scratch: the rows of each expert that are placed so far.
+// mode 0: scores sigmoid(logit), the rows of xs are the tokens' times their weights.  mode 1: scores softmax(logits), the
+// choice by score + correction [experts] (float32 or null), weights the chosen scores over their sum times route_scale;
+// the rows of xs are the tokens' as they are and fms_route_gather takes the weights.
 FMS_API int fms_route(const void* x, int dtype, const void* router, int router_dtype, int* expert, float* weight, int* counts,
                       int* offsets, int* tile_first, int* row_of_pair, int* group_of_row, void* xs, int n_tokens, int dim,
-                      int experts, int top, cudaStream_t stream) {
+                      int experts, int top, int mode, const float* correction, float route_scale, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (dim <= 0 || experts <= 0 || top <= 0 || top > experts) return fms_fail("route: dim %d, experts %d, top %d", dim, experts, top);
-  const size_t smem = ((size_t)dim + experts) * sizeof(float);
+  if (mode != 0 && mode != 1) return fms_fail("route: mode %d", mode);
+  const size_t smem = ((size_t)dim + 2 * (size_t)experts) * sizeof(float);
   if (smem > 200 * 1024) return fms_fail("route: rows of %d values and %d experts do not fit shared memory", dim, experts);
   FMS_DISPATCH_DTYPE(dtype, T, FMS_DISPATCH_DTYPE(router_dtype, TW, {
     if (smem > 48 * 1024) cudaFuncSetAttribute(route_kernel<T, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     fms_launch(route_kernel<T, TW>, dim3(n_tokens), dim3(32 * ROUTE_WARPS), smem, stream, (const T*)x, (const TW*)router, expert, weight,
-               dim, experts, top);
+               dim, experts, top, mode, correction, route_scale);
   }));
   if (fms_launch_status("route")) return 1;
   const int n_pairs = n_tokens * top;
@@ -444,8 +493,46 @@ FMS_API int fms_route(const void* x, int dtype, const void* router, int router_d
   FMS_DISPATCH_DTYPE(dtype, T,
                      fms_launch(route_scatter_kernel<T>, dim3(n_pairs), dim3(128), 0, stream, (const T*)x, (const int*)expert,
                                 (const float*)weight, (const int*)offsets, counts, row_of_pair, group_of_row, (T*)xs, dim,
-                                top, experts, n_pairs));
+                                top, experts, n_pairs, mode == 0 ? 1 : 0));
   return fms_launch_status("route (scatter)");
+}
+
+// y = relu(y)^2 in place: the activation of ungated experts after a library product
+template <typename T>
+__global__ void relu_squared_kernel(T* y, size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+    y[i] = from_f32<T>(activated(to_f32(y[i]), 2));
+}
+
+__global__ void relu_squared_vec_kernel(__nv_bfloat16* y, size_t total8) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total8; i += (size_t)gridDim.x * blockDim.x) {
+    float v[8];
+    rows_load8(y + 8 * i, v);
+    uint32_t o[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      __nv_bfloat162 b = __floats2bfloat162_rn(activated(v[2 * k], 2), activated(v[2 * k + 1], 2));
+      o[k] = *reinterpret_cast<uint32_t*>(&b);
+    }
+    *reinterpret_cast<uint4*>(y + 8 * i) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+FMS_API int fms_relu_squared(void* y, int dtype, long total, cudaStream_t stream) {
+  if (total <= 0) return 0;
+  if (dtype == FMS_BF16 && total % 8 == 0 && ((uintptr_t)y & 15) == 0) {
+    const long total8 = total / 8;
+    const int blocks = (int)((total8 + 255) / 256 < 148 * 32 ? (total8 + 255) / 256 : 148 * 32);
+    fms_launch(relu_squared_vec_kernel, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)y, (size_t)total8);
+    return fms_launch_status("relu_squared");
+  }
+  const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  FMS_DISPATCH_DTYPE(dtype, T, fms_launch(relu_squared_kernel<T>, dim3(blocks), dim3(256), 0, stream, (T*)y, (size_t)total));
+  return fms_launch_status("relu_squared");
 }
 
 FMS_API int fms_gated_clamped(const void* gu, void* out, int dtype, int n_rows, int hidden, float limit, float alpha,
@@ -466,11 +553,12 @@ FMS_API int fms_gated_clamped(const void* gu, void* out, int dtype, int n_rows, 
   return fms_launch_status("gated_clamped");
 }
 
+// weight: [n_tokens, top] float32 that multiply the pairs' rows, or null for their plain sum
 FMS_API int fms_route_gather(const void* ys, int dtype, const int* row_of_pair, void* out, int n_tokens, int dim, int top,
-                             cudaStream_t stream) {
+                             const float* weight, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   FMS_DISPATCH_DTYPE(dtype, T,
-                     fms_launch(route_gather_kernel<T>, dim3(n_tokens), dim3(256), sizeof(int) * top, stream, (const T*)ys, row_of_pair,
-                                (T*)out, dim, top, n_tokens * top));
+                     fms_launch(route_gather_kernel<T>, dim3(n_tokens), dim3(256), 2 * sizeof(int) * top, stream, (const T*)ys, row_of_pair,
+                                (T*)out, dim, top, n_tokens * top, weight));
   return fms_launch_status("route_gather");
 }

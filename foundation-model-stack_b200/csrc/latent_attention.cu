@@ -8,7 +8,8 @@
 // Scores, softmax and sums are float32.  The cache is the block cache of the other attention kernels with one
 // key head of rank + rot values and no value plane.
 //
-// latent_prepare: from the fused projection [q heads (dim + rot each) | c (rank) | kr (rot) | gates (heads)] of a
+// latent_prepare (c and kr may also come from a matrix of their own, `kv`; pairs by halves and a constant on the sines
+// and cosines are options): from the fused projection [q heads (dim + rot each) | c (rank) | kr (rot) | gates (heads)] of a
 // step's rows it norms c (RMS, a gain per value), rotates kr and every head's rot part by the row's position
 // (adjacent pairs (2i, 2i+1), the first rot_dims values, angle = position * inv_freq[i], float32), writes [c | kr]
 // into the cache at the row's slot and place and the rotated query parts into q_full[:, h, rank:].
@@ -29,13 +30,29 @@ constexpr int KT = 32;      // keys brought into shared memory at a time
 constexpr int HG = 8;       // heads a block takes
 constexpr int THREADS = 256;
 
+// Value j (< 2 half) of a rotated run: pairs (2i, 2i + 1), or with `halves` (i, i + half), turned by position * inv_freq[i];
+// rot_mult multiplies sine and cosine (1 for a plain rotation).
+template <typename T>
+__device__ __forceinline__ float rotated(const T* src, int j, int half, int halves, float position, const float* inv_freq,
+                                         float rot_mult) {
+  const int pair = halves ? (j < half ? j : j - half) : j >> 1;
+  const bool second = halves ? j >= half : (j & 1);
+  float sn, cs;
+  sincosf(position * inv_freq[pair], &sn, &cs);
+  sn *= rot_mult;
+  cs *= rot_mult;
+  const float a = to_f32(src[halves ? pair : 2 * pair]), b = to_f32(src[halves ? pair + half : 2 * pair + 1]);
+  return second ? b * cs + a * sn : a * cs - b * sn;
+}
+
 template <typename T, typename TG>
 __global__ void __launch_bounds__(128) latent_prepare_kernel(
     const T* __restrict__ proj, int proj_width, T* __restrict__ q_full, const TG* __restrict__ c_gain, float eps,
     const float* __restrict__ inv_freq, int rot_dims, const int* __restrict__ positions,
     const int* __restrict__ position_ids, const int* __restrict__ token_seq, const int* __restrict__ slots,
     T* __restrict__ cache, const int* __restrict__ table, int table_stride, int block_tokens, int heads, int dim, int rot,
-    int rank, int write_cache, int n_seqs, int n_slots, int n_blocks, int* __restrict__ error_flag) {
+    int rank, int write_cache, int n_seqs, int n_slots, int n_blocks, int* __restrict__ error_flag, int halves,
+    float rot_mult, const T* __restrict__ kv, int kv_width) {
   __shared__ float scratch[33];
   pdl_launch_dependents();
   pdl_wait();
@@ -51,11 +68,7 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(
     const T* src = row + (size_t)h * (dim + rot) + dim;
     float v;
     if (j < 2 * half) {
-      const int pair = j >> 1;
-      float sn, cs;
-      sincosf(position * inv_freq[pair], &sn, &cs);
-      const float a = to_f32(src[2 * pair]), b = to_f32(src[2 * pair + 1]);
-      v = (j & 1) ? b * cs + a * sn : a * cs - b * sn;
+      v = rotated(src, j, half, halves, position, inv_freq, rot_mult);
     } else {
       v = to_f32(src[j]);
     }
@@ -73,7 +86,9 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(
     return;
   }
   T* dst = cache + ((size_t)blk * block_tokens + pos % block_tokens) * width;
-  const T* c = row + q_cols;
+  // [c | kr] follow the queries in the row, or are the first columns of a matrix of their own (queries that come from
+  // another projection)
+  const T* c = kv ? kv + (size_t)t * kv_width : row + q_cols;
   float ss = 0.f;
   for (int d = threadIdx.x; d < rank; d += blockDim.x) {
     const float v = to_f32(c[d]);
@@ -85,16 +100,31 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(
   for (int j = threadIdx.x; j < rot; j += blockDim.x) {
     float v;
     if (j < 2 * half) {
-      const int pair = j >> 1;
-      float sn, cs;
-      sincosf(position * inv_freq[pair], &sn, &cs);
-      const float a = to_f32(kr[2 * pair]), b = to_f32(kr[2 * pair + 1]);
-      v = (j & 1) ? b * cs + a * sn : a * cs - b * sn;
+      v = rotated(kr, j, half, halves, position, inv_freq, rot_mult);
     } else {
       v = to_f32(kr[j]);
     }
     dst[rank + j] = from_f32<T>(v);
   }
+}
+
+// A run of columns of a wider matrix, normed row by row: out[t, :n] = x[t, off : off + n] / sqrt(mean(.^2) + eps) * gain
+// (queries that go through a latent of their own).  A warp a row, four rows a block; float32 arithmetic.
+template <typename T, typename TG>
+__global__ void __launch_bounds__(128) latent_query_norm_kernel(const T* x, int stride, int n, const TG* gain, float eps,
+                                                               T* out, int n_tokens) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (t >= n_tokens) return;
+  const T* row = x + (size_t)t * stride;
+  float ss = 0.f;
+  for (int d = lane; d < n; d += 32) {
+    const float v = to_f32(row[d]);
+    ss += v * v;
+  }
+  const float inv = 1.f / sqrtf(warp_sum(ss) / (float)n + eps);
+  for (int d = lane; d < n; d += 32) out[(size_t)t * n + d] = from_f32<T>(to_f32(row[d]) * inv * to_f32(gain[d]));
 }
 
 struct LatentArgs {
@@ -112,6 +142,7 @@ struct LatentArgs {
   long gate_stride;
   int table_stride, block_tokens, heads, rank, rot, n_splits, n_seqs, n_slots, n_blocks;
   float scale;
+  int window;  // > 0: the row at position p sees the keys p - window + 1 .. p only
 };
 
 // One block per (row, split of keys, group of HG heads).  Keys come KT at a time into shared memory as float32; a warp
@@ -137,8 +168,10 @@ __global__ void __launch_bounds__(THREADS) latent_attention_kernel(LatentArgs a)
   const int slot = a.slots[seq];
   if (!FMS_IN(slot, a.n_slots)) return;
   const bool whole = a.n_splits == 1;  // one split takes all keys and writes the result itself
-  const int lo = whole ? 0 : split * SPLIT;
-  const int hi = whole ? pos + 1 : min(pos + 1, lo + SPLIT);
+  const int seen = a.window > 0 ? max(0, pos - a.window + 1) : 0;  // the first key this row sees
+  const int hi = whole ? pos + 1 : min(pos + 1, split * SPLIT + SPLIT);
+  if (hi <= seen) return;  // a split before the window: the merge does not look at it
+  const int lo = max(whole ? 0 : split * SPLIT, seen / KT * KT);  // tiles stay aligned; keys before `seen` are masked
   const T* q = (const T*)a.q + ((size_t)t * a.heads + h0) * width;
   for (int i = threadIdx.x; i < nh * width; i += THREADS) qs[i] = to_f32(q[i]);
   float acc[NACC];
@@ -161,7 +194,8 @@ __global__ void __launch_bounds__(THREADS) latent_attention_kernel(LatentArgs a)
     __syncthreads();
     if (warp < nh) {
       float s = -INFINITY;
-      if (lane < nk) {
+      const bool counts = lane < nk && k0 + lane >= seen;
+      if (counts) {
         const float* qh = qs + warp * width;
         const float* kj = ks + lane * kstride;
         float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;  // four chains: none waits for the one before
@@ -176,8 +210,8 @@ __global__ void __launch_bounds__(THREADS) latent_attention_kernel(LatentArgs a)
         s = ((d0 + d1) + (d2 + d3)) * a.scale;
       }
       const float m_new = fmaxf(m_run, warp_max(s));
-      const float p = lane < nk ? expf(s - m_new) : 0.f;
-      const float al = expf(m_run - m_new);  // 0 the first time
+      const float p = counts ? expf(s - m_new) : 0.f;
+      const float al = m_run == -INFINITY ? 0.f : expf(m_run - m_new);  // 0 the first time
       l_run = l_run * al + warp_sum(p);
       m_run = m_new;
       ps[warp * KT + lane] = p;
@@ -241,17 +275,18 @@ __global__ void __launch_bounds__(128) latent_combine_kernel(LatentArgs a) {
   const int t = blockIdx.x, h = blockIdx.y;
   const int pos = ld_fresh(a.positions + t);
   const int used = min(a.n_splits, pos / SPLIT + 1);
+  const int s_lo = a.window > 0 ? min(max(0, pos - a.window + 1) / SPLIT, used - 1) : 0;  // splits before the window hold nothing
   const size_t at = ((size_t)t * a.heads + h) * a.n_splits;
   float m = a.sink ? to_f32(((const TS*)a.sink)[h]) : -INFINITY;
-  for (int s = 0; s < used; ++s) m = fmaxf(m, a.part_ml[2 * (at + s)]);
+  for (int s = s_lo; s < used; ++s) m = fmaxf(m, a.part_ml[2 * (at + s)]);
   float denom = a.sink ? expf(to_f32(((const TS*)a.sink)[h]) - m) : 0.f;
-  for (int s = 0; s < used; ++s) denom += a.part_ml[2 * (at + s) + 1] * expf(a.part_ml[2 * (at + s)] - m);
+  for (int s = s_lo; s < used; ++s) denom += a.part_ml[2 * (at + s) + 1] * expf(a.part_ml[2 * (at + s)] - m);
   float f = 1.f / denom;
   if (a.gate) f *= 1.f / (1.f + expf(-to_f32(((const T*)a.gate)[(size_t)t * a.gate_stride + h])));
   T* o = (T*)a.out + ((size_t)t * a.heads + h) * a.rank;
   for (int d = threadIdx.x; d < a.rank; d += blockDim.x) {
     float v = 0.f;
-    for (int s = 0; s < used; ++s) v = fmaf(a.part_o[(at + s) * a.rank + d], expf(a.part_ml[2 * (at + s)] - m), v);
+    for (int s = s_lo; s < used; ++s) v = fmaf(a.part_o[(at + s) * a.rank + d], expf(a.part_ml[2 * (at + s)] - m), v);
     o[d] = from_f32<T>(v * f);
   }
 }
@@ -313,9 +348,11 @@ __global__ void __launch_bounds__(256) latent_prefill_mma_kernel(LatentArgs a, c
   const int ntok = min(tq, first_row[seq + 1] - first);
   if (ntok <= 0) return;
   const int last_pos = ld_fresh(a.positions + first + ntok - 1);
-  const int kt_lo = a.n_splits > 1 ? split * (SPLIT / MK) : 0;
-  const int n_kt = a.n_splits > 1 ? min(last_pos / MK + 1, kt_lo + SPLIT / MK) : last_pos / MK + 1;
-  if (kt_lo >= n_kt) return;  // a split beyond the sequence: the merge does not look at it
+  const int first_pos = ld_fresh(a.positions + first);
+  const int seen = a.window > 0 ? max(0, first_pos - a.window + 1) : 0;  // the first key that any row of the tile sees
+  const int kt_lo = max(a.n_splits > 1 ? split * (SPLIT / MK) : 0, seen / MK);
+  const int n_kt = a.n_splits > 1 ? min(last_pos / MK + 1, (split + 1) * (SPLIT / MK)) : last_pos / MK + 1;
+  if (kt_lo >= n_kt) return;  // a split beyond the sequence or before the window: the merge does not look at it
   if (tid < MR) {
     const int tok = tid / hb, hh = tid - tok * hb;
     pos_s[tid] = (tok < ntok && h0 + hh < a.heads) ? ld_fresh(a.positions + first + tok) : -1;
@@ -380,7 +417,8 @@ __global__ void __launch_bounds__(256) latent_prefill_mma_kernel(LatentArgs a, c
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int key = kt * MK + sub * 4 + j;
-        sv[j] = key <= pos ? ss[r * (MK + 1) + sub * 4 + j] * a.scale : -INFINITY;
+        const bool counts = key <= pos && (a.window <= 0 || key > pos - a.window);
+        sv[j] = counts ? ss[r * (MK + 1) + sub * 4 + j] * a.scale : -INFINITY;
         mx = fmaxf(mx, sv[j]);
       }
 #pragma unroll
@@ -505,12 +543,23 @@ int launch_attention(const LatentArgs& a, int n_tokens, cudaStream_t stream) {
 
 FMS_API int fms_latent_split_tokens() { return SPLIT; }
 
+// x: the first of the n columns to norm in row 0 of a matrix with rows of `stride` values; out [n_tokens, n]
+FMS_API int fms_latent_query_norm(const void* x, int dtype, int stride, int n, const void* gain, int gain_dtype, float eps,
+                                  void* out, int n_tokens, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (n <= 0 || stride < n) return fms_fail("latent_query_norm: %d columns of rows of %d", n, stride);
+  FMS_DISPATCH_DTYPE(dtype, T, FMS_DISPATCH_DTYPE(gain_dtype, TG,
+                     fms_launch(latent_query_norm_kernel<T, TG>, dim3((n_tokens + 3) / 4), dim3(128), 0, stream, (const T*)x,
+                                stride, n, (const TG*)gain, eps, (T*)out, n_tokens)));
+  return fms_launch_status("latent_query_norm");
+}
+
 FMS_API int fms_latent_prepare(const void* proj, int dtype, int proj_width, void* q_full, const void* c_gain, int gain_dtype,
                                float eps, const float* inv_freq, int rot_dims, const int* positions,
                                const int* position_ids, const int* token_seq, const int* slots, void* cache,
                                const int* table, int table_stride, int block_tokens, int n_tokens, int heads, int dim,
                                int rot, int rank, int write_cache, int n_seqs, int n_slots, int n_blocks, int* error_flag,
-                               cudaStream_t stream) {
+                               int halves, float rot_mult, const void* kv, int kv_width, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (heads <= 0 || dim < 0 || rot < 0 || rank <= 0 || rot_dims < 0 || rot_dims > rot || (rot_dims & 1))
     return fms_fail("latent_prepare: heads %d, dim %d, rot %d (%d rotated), rank %d", heads, dim, rot, rot_dims, rank);
@@ -518,7 +567,8 @@ FMS_API int fms_latent_prepare(const void* proj, int dtype, int proj_width, void
                      fms_launch(latent_prepare_kernel<T, TG>, dim3(n_tokens), dim3(128), 0, stream, (const T*)proj,
                                 proj_width, (T*)q_full, (const TG*)c_gain, eps, inv_freq, rot_dims, positions,
                                 position_ids, token_seq, slots, (T*)cache, table, table_stride, block_tokens, heads, dim,
-                                rot, rank, write_cache, n_seqs, n_slots, n_blocks, error_flag)));
+                                rot, rank, write_cache, n_seqs, n_slots, n_blocks, error_flag, halves, rot_mult,
+                                (const T*)kv, kv_width)));
   return fms_launch_status("latent_prepare");
 }
 
@@ -528,7 +578,7 @@ FMS_API int fms_latent_attention(const void* q, void* out, int dtype, const void
                                  const void* sink, int sink_dtype, const int* table, int table_stride, int block_tokens,
                                  const int* slots, const int* token_seq, const int* positions, int n_tokens, int n_splits,
                                  float* part_o, float* part_ml, int heads, int rank, int rot, float scale, int n_seqs,
-                                 int n_slots, int n_blocks, cudaStream_t stream) {
+                                 int n_slots, int n_blocks, int window, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (n_splits < 1 || (n_splits > 1 && (part_o == nullptr || part_ml == nullptr)))
     return fms_fail("latent_attention: %d splits without scratch", n_splits);
@@ -537,6 +587,7 @@ FMS_API int fms_latent_attention(const void* q, void* out, int dtype, const void
   a.token_seq = token_seq; a.positions = positions; a.part_o = part_o; a.part_ml = part_ml; a.gate_stride = gate_stride;
   a.table_stride = table_stride; a.block_tokens = block_tokens; a.heads = heads; a.rank = rank; a.rot = rot;
   a.n_splits = n_splits; a.n_seqs = n_seqs; a.n_slots = n_slots; a.n_blocks = n_blocks; a.scale = scale;
+  a.window = window > 0 ? window : 0;
   FMS_DISPATCH_DTYPE(dtype, T, FMS_DISPATCH_DTYPE(sink ? sink_dtype : dtype, TS, return launch_attention<T, TS>(a, n_tokens, stream)));
   return 0;
 }
@@ -550,7 +601,7 @@ FMS_API int fms_latent_attention_prefill_bf16(const void* q, void* out, const vo
                                               const int* positions, const int* tiles, int n_tiles, int tile_tokens,
                                               int heads_per_block, int heads, int rank, int rot, float scale, int n_seqs,
                                               int n_slots, int n_blocks, const int* token_seq, int n_splits, float* part_o,
-                                              float* part_ml, cudaStream_t stream) {
+                                              float* part_ml, int window, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (n_splits < 1 || (n_splits > 1 && (tile_tokens != 1 || part_o == nullptr || part_ml == nullptr || token_seq == nullptr)))
     return fms_fail("latent_attention_prefill: %d splits need one token a tile and scratch", n_splits);
@@ -562,6 +613,7 @@ FMS_API int fms_latent_attention_prefill_bf16(const void* q, void* out, const vo
   a.token_seq = token_seq; a.positions = positions; a.part_o = part_o; a.part_ml = part_ml; a.gate_stride = gate_stride;
   a.table_stride = table_stride; a.block_tokens = block_tokens; a.heads = heads; a.rank = rank; a.rot = rot;
   a.n_splits = n_splits; a.n_seqs = n_seqs; a.n_slots = n_slots; a.n_blocks = n_blocks; a.scale = scale;
+  a.window = window > 0 ? window : 0;
   const int rowb = width * 2 + 16;
   const size_t smem = (size_t)(MR + 2 * MK) * rowb + MR * (MK + 1) * 4 + MR * (MK * 2 + 16) + MR * 16;
   dim3 grid(n_tiles, (heads + heads_per_block - 1) / heads_per_block, n_splits);

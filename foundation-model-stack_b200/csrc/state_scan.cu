@@ -378,10 +378,12 @@ __global__ void __launch_bounds__(SCAN_THREADS) selective_scan_kernel(const floa
 //   qkv [tokens, 2 kvheads * dim + heads * vdim] float32 (after the convolution): q | k | v;  q and k of every key head
 //   become unit vectors in place, x / sqrt(sum(x^2) + 1e-6), q also times dim^-1/2
 //   decay[t, h, n] = exp(-exp(a_log[h]) * softplus(a_raw[t, h, n] + dt_bias[h, n]));  beta[t, h] = sigmoid(beta_raw[t, h])
+//   `per_head`: one decay a head, exp(-exp(a_log[h]) * softplus(a_raw[t, h] + dt_bias[h])), written to all its channels
+//   a_raw is walked by its row stride `a_stride`
 template <typename T>
-__global__ void delta_prepare_kernel(float* qkv, const T* a_raw, const T* beta_raw, int beta_stride, const float* dt_bias,
-                                     const float* a_log, float* decay, float* beta, int heads, int kvheads, int dim,
-                                     int vdim) {
+__global__ void delta_prepare_kernel(float* qkv, const T* a_raw, int a_stride, int per_head, const T* beta_raw,
+                                     int beta_stride, const float* dt_bias, const float* a_log, float* decay, float* beta,
+                                     int heads, int kvheads, int dim, int vdim) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x, lane = threadIdx.x & 31;
@@ -399,8 +401,14 @@ __global__ void delta_prepare_kernel(float* qkv, const T* a_raw, const T* beta_r
       const int h = item - 2 * kvheads;
       const double A = exp((double)a_log[h]);  // decays compound over a sequence: taken in double, rounded once
       const size_t at = ((size_t)t * heads + h) * dim;
-      for (int n = lane; n < dim; n += 32)
-        decay[at + n] = (float)exp(-A * softplus_d((double)to_f32(a_raw[at + n]) + (double)dt_bias[(size_t)h * dim + n]));
+      if (per_head) {
+        const float d = (float)exp(-A * softplus_d((double)to_f32(a_raw[(size_t)t * a_stride + h]) + (double)dt_bias[h]));
+        for (int n = lane; n < dim; n += 32) decay[at + n] = d;
+      } else {
+        const T* ar = a_raw + (size_t)t * a_stride + (size_t)h * dim;
+        for (int n = lane; n < dim; n += 32)
+          decay[at + n] = (float)exp(-A * softplus_d((double)to_f32(ar[n]) + (double)dt_bias[(size_t)h * dim + n]));
+      }
       if (lane == 0) beta[(size_t)t * heads + h] = sigmoid_f(to_f32(beta_raw[(size_t)t * beta_stride + h]));
     }
   }
@@ -784,6 +792,7 @@ __global__ void gated_group_rmsnorm_kernel(const float* x, const T* gate, int ga
       if (gate_mode == 1) v[k] *= z[k] * sigmoid_f(z[k]);
       v[k] = v[k] * inv * weight[(c0 + e + k) % weight_period];
       if (gate_mode == 2) v[k] *= sigmoid_f(z[k]);
+      if (gate_mode == 3) v[k] *= z[k] * sigmoid_f(z[k]);
       v[k] *= factor;
     }
     if constexpr (VEC == 4) st4(out + t * width + c0 + e, v);
@@ -913,16 +922,17 @@ FMS_API int fms_selective_scan(const float* xbc, const void* dt_raw, int dtype, 
   return fms_launch_status("selective_scan");
 }
 
-// decay [tokens, heads * dim] and beta [tokens, heads]: float32 scratch of the caller's
+// decay [tokens, heads * dim] and beta [tokens, heads]: float32 scratch of the caller's.  a_raw: rows of a_stride
+// values, of which the first heads * dim (per_head: the first heads) are the decays' logits
 FMS_API int fms_delta_rule_scan(float* qkv, const void* beta_raw, int dtype, int beta_stride, const void* a_raw,
-                                const float* dt_bias, const float* a_log, float* decay, float* beta, float* state, float* o,
+                                int a_stride, int per_head, const float* dt_bias, const float* a_log, float* decay, float* beta, float* state, float* o,
                                 const int* first_row, const int* slots, int n_tokens, int n_seqs, int heads, int kvheads,
                                 int dim, int vdim, int write_state, int n_slots, cudaStream_t stream) {
   if (n_seqs <= 0 || n_tokens <= 0) return 0;
   if (heads <= 0 || kvheads <= 0 || heads % kvheads || dim <= 0 || dim > 256 || vdim <= 0)
     return fms_fail("delta_rule_scan: %d heads over %d, dim %d (up to 256), vdim %d", heads, kvheads, dim, vdim);
   FMS_DISPATCH_DTYPE(dtype, T, fms_launch(delta_prepare_kernel<T>, dim3(n_tokens, (2 * kvheads + heads + 3) / 4), dim3(128), 0, stream, qkv, (const T*)a_raw,
-                                          (const T*)beta_raw, beta_stride, dt_bias, a_log, decay, beta, heads, kvheads, dim,
+                                          a_stride, per_head, (const T*)beta_raw, beta_stride, dt_bias, a_log, decay, beta, heads, kvheads, dim,
                                           vdim));
   const ScanShape shape = scan_shape(n_seqs, heads, vdim, dim);
   const int vb = SCAN_THREADS / shape.parts * shape.vp;  // value columns of a block

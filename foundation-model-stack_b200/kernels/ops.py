@@ -56,18 +56,21 @@ _SIGNATURES = {
     "fms_normed_add_rmsnorm": [_P, _P, _I, _P, _F, _F, _P, _F, _F, _I, _P, _I, _P, _I, _I, _I, _P],
     "fms_mingru_scan": [_P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _I, _P, _P],
     "fms_grouped_linear": [_P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _L, _I, _F, _F, _I, _P],
-    "fms_route": [_P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
-    "fms_route_gather": [_P, _I, _P, _P, _I, _I, _I, _P],
+    "fms_route": [_P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _F, _P],
+    "fms_route_gather": [_P, _I, _P, _P, _I, _I, _I, _P, _P],
+    "fms_relu_squared": [_P, _I, _L, _P],
     "fms_gated_clamped": [_P, _P, _I, _I, _I, _F, _F, _P],
     "fms_latent_attention_prefill_bf16": [_P, _P, _P, _P, _L, _P, _I, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I,
-                                          _F, _I, _I, _I, _P, _I, _P, _P, _P],
+                                          _F, _I, _I, _I, _P, _I, _P, _P, _I, _P],
     "fms_latent_prepare": [_P, _I, _I, _P, _P, _I, _F, _P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I,
-                           _I, _I, _P, _P],
+                           _I, _I, _P, _I, _F, _P, _I, _P],
+    "fms_latent_query_norm": [_P, _I, _I, _I, _P, _I, _F, _P, _I, _P],
     "fms_latent_attention": [_P, _P, _I, _P, _P, _L, _P, _I, _P, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _F, _I,
-                             _I, _I, _P],
+                             _I, _I, _I, _P],
     "fms_scaled_add_rmsnorm": [_P, _F, _P, _F, _P, _F, _P, _I, _F, _P, _I, _I, _I, _P],
     "fms_cast_rows": [_P, _P, _I, _L, _P],
-    "fms_qk_prepare_store": [_P, _I, _I, _P, _P, _I, _I, _F, _P, _P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I,
+    "fms_parts_group_rmsnorm": [_P, _P, _F, _P, _F, _P, _F, _P, _F, _P, _P, _F, _I, _P, _P, _I, _P, _I, _I, _I, _P],
+    "fms_qk_prepare_store": [_P, _I, _I, _P, _P, _I, _F, _I, _F, _P, _P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I,
                              _I, _I, _I, _I, _I, _P, _I, _I, _I, _P],
     "fms_sigmoid_gate": [_P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _P],
     "fms_normed_add_norm": [_P, _P, _I, _P, _F, _I, _P, _F, _P, _I, _P, _I, _I, _I, _P],
@@ -75,11 +78,15 @@ _SIGNATURES = {
     "fms_decay_scan": [_P, _P, _I, _I, _P, _F, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "fms_attention_prefill_sink": [_P, _P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P, _P,
                                    _P],
+    "fms_attention_prefill_masked": [_P, _P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P, _P,
+                                     _I, _F, _P],
+    "fms_attention_decode_masked": [_P, _P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _F, _I, _I, _I, _L,
+                                    _P, _P, _P, _I, _F, _P],
     "fms_attention_decode_sink": [_P, _P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _F, _I, _I, _I, _L,
                                   _P, _P, _P, _P],
     "fms_causal_conv": [_P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "fms_selective_scan": [_P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
-    "fms_delta_rule_scan": [_P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "fms_delta_rule_scan": [_P, _P, _I, _I, _P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "fms_gated_group_rmsnorm": [_P, _P, _I, _I, _I, _P, _I, _F, _F, _P, _I, _I, _I, _P],
     "fms_argmax": [_P, _P, _I, _I, _P],
     "fms_sample": [_P, _P, _I, _I, _F, _I, _U64, _P, _I, _P],
@@ -305,6 +312,32 @@ def scaled_add_rmsnorm(residual: torch.Tensor, alpha: float, parts, gain: torch.
     _call("elementwise", "fms_scaled_add_rmsnorm", _ptr(residual), float(alpha), _ptr(da), float(sa), _ptr(db), float(sb),
           _ptr(gain), _code(gain.dtype), float(eps), _ptr(copy), _code(out_dtype), n, dim, _stream())
     return copy
+
+
+def parts_group_rmsnorm(residual: torch.Tensor, parts, gains, eps: float, groups: int, out_dtype: torch.dtype,
+                        rows: Optional[torch.Tensor] = None):
+    """residual (float32, in place) += sum of factor * delta over ``parts`` (up to four (delta, factor), deltas in
+    ``out_dtype``); then the row in ``groups`` equal consecutive runs, each divided by its own root mean square, and
+    one output per entry of ``gains`` (one or two float32 vectors of the row's width): the normed row times that gain,
+    in ``out_dtype``.  Two norms of the same stream so share one pass and one set of statistics.  With ``rows`` only
+    those rows are computed and the residual is not written.  Returns the list of outputs."""
+    dim = residual.shape[1]
+    n = rows.shape[0] if rows is not None else residual.shape[0]
+    parts = [(d, float(f)) for d, f in (parts or []) if d is not None]
+    if residual.dtype != torch.float32:
+        raise KernelError("the residual stream is float32")
+    if len(parts) > 4 or any(d.dtype != out_dtype or tuple(d.shape) != tuple(residual.shape) for d, _ in parts):
+        raise KernelError("parts_group_rmsnorm: up to four sublayer outputs of the stream's shape, in the compute dtype")
+    if not 1 <= len(gains) <= 2 or any(g.dtype != torch.float32 or g.shape[0] != dim for g in gains):
+        raise KernelError("parts_group_rmsnorm: one or two float32 gains of the row's width")
+    outs = [torch.empty((n, dim), dtype=out_dtype, device=residual.device) for _ in gains]
+    flat = []
+    for i in range(4):
+        flat += [_ptr(parts[i][0]), parts[i][1]] if i < len(parts) else [None, 0.0]
+    _call("elementwise", "fms_parts_group_rmsnorm", _ptr(residual), *flat, _ptr(gains[0]),
+          _ptr(gains[1]) if len(gains) > 1 else None, float(eps), int(groups), _ptr(outs[0]),
+          _ptr(outs[1]) if len(outs) > 1 else None, _code(out_dtype), _ptr(rows), n, dim, residual.shape[0], _stream())
+    return outs
 
 
 def cast_rows(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
@@ -561,13 +594,15 @@ def attention_constants(head_dim: int, dtype: torch.dtype, nheads: int, kvheads:
 def qk_prepare_store(proj: torch.Tensor, inv_freq: Optional[torch.Tensor], rot: int, qk_norm: bool, eps: float, batch,
                      view, nheads: int, kvheads: int, dim: int, vdim: int, pad: int,
                      writes_cache: bool = True, norm_first: bool = False, q_gain: Optional[torch.Tensor] = None,
-                     k_gain: Optional[torch.Tensor] = None, halves: bool = False, values_are_keys: bool = False) -> torch.Tensor:
+                     k_gain: Optional[torch.Tensor] = None, halves: bool = False, values_are_keys: bool = False,
+                     rot_mult: float = 1.0) -> torch.Tensor:
     """From rows [q: nheads x dim | k: kvheads x dim | v: kvheads x vdim | ...] of ``proj``: rotates the first ``rot``
     values of every q and k head by the row's position (adjacent pairs; with ``halves`` value i with value i + rot / 2),
     divides q and k by their root mean square over ``dim`` where ``qk_norm`` (after the rotation; with ``norm_first``
     before it, and then times ``q_gain`` / ``k_gain``, float32 [dim], where given), writes k and v into the cache (heads
     of ``pad`` values there, zeros beyond dim and vdim) and returns q [tokens, nheads * pad], padded alike.
-    ``values_are_keys``: the rows have no v columns; a value is its key as projected, before norm and rotation."""
+    ``values_are_keys``: the rows have no v columns; a value is its key as projected, before norm and rotation.
+    ``rot_mult`` multiplies the rotation's sines and cosines (stretched frequencies come with such a constant)."""
     n = proj.shape[0]
     for g in (q_gain, k_gain):
         if g is not None and (g.dtype != torch.float32 or g.shape[0] != dim):
@@ -577,7 +612,8 @@ def qk_prepare_store(proj: torch.Tensor, inv_freq: Optional[torch.Tensor], rot: 
                           f"heads of {pad}")
     q = torch.empty((n, nheads * pad), dtype=proj.dtype, device=proj.device)
     _call("elementwise", "fms_qk_prepare_store", _ptr(proj), _code(proj.dtype), proj.shape[1], _ptr(q), _ptr(inv_freq),
-          int(rot), 1 if qk_norm else 0, float(eps), _ptr(q_gain), _ptr(k_gain), 1 if norm_first else 0, 1 if halves else 0,
+          int(rot), float(rot_mult), 1 if qk_norm else 0, float(eps), _ptr(q_gain), _ptr(k_gain), 1 if norm_first else 0,
+          1 if halves else 0,
           1 if values_are_keys else 0, _ptr(batch.positions), _ptr(getattr(batch, "position_ids", None)),
           _ptr(batch.token_seq), _ptr(batch.slots), _ptr(view.keys), _ptr(view.values), _ptr(view.table),
           view.table.shape[1], view.block_tokens, n, nheads, kvheads, dim, vdim, pad, 1 if writes_cache else 0,
@@ -599,10 +635,16 @@ def sigmoid_gate(o: torch.Tensor, gate: Optional[torch.Tensor], gate_offset: int
 
 
 def attention(q: torch.Tensor, batch, view, nheads: int, kvheads: int, head_dim: int, scale: float,
-              window: int, sink: Optional[torch.Tensor] = None) -> torch.Tensor:
+              window: int, sink: Optional[torch.Tensor] = None, chunk: int = 0, softcap: float = 0.0) -> torch.Tensor:
     """Causal softmax attention of the step's queries over the cache (which already holds the step's own
     keys and values).  One query per sequence takes the split-key decode kernels, else the prefill kernel.
-    ``sink`` [nheads] float32: a term exp(sink[h]) in every row's denominator that belongs to no key."""
+    ``sink`` [nheads] float32: a term exp(sink[h]) in every row's denominator that belongs to no key.
+    ``chunk`` > 0: the positions of a sequence are cut into runs of ``chunk``, counted from its position 0, and a query
+    sees the keys of its own run only (not together with a window).  ``softcap`` > 0: a score s becomes
+    softcap * tanh(s / softcap) after the scale."""
+    masked = bool(chunk) or bool(softcap)
+    if chunk < 0 or softcap < 0 or (chunk and window):
+        raise KernelError(f"attention: chunk {chunk}, window {window}, softcap {softcap}")
     if sink is not None and (sink.dtype != torch.float32 or sink.shape[0] != nheads):
         raise KernelError("attention: the sinks are float32, one per head")
     out = torch.empty_like(q)
@@ -615,8 +657,9 @@ def attention(q: torch.Tensor, batch, view, nheads: int, kvheads: int, head_dim:
         part_o = torch.empty((batch.n_seqs, nheads, n_splits, head_dim), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((batch.n_seqs, nheads, n_splits, 2), dtype=torch.float32, device=q.device)
         # total_len (what the host knows of the sequences' lengths) chooses between the two bfloat16 decode kernels
-        tail = () if sink is None else (_ptr(sink),)
-        _call(lib, "fms_attention_decode" if sink is None else "fms_attention_decode_sink", *common, batch.n_seqs,
+        tail = (_ptr(sink), int(chunk), float(softcap)) if masked else (() if sink is None else (_ptr(sink),))
+        _call(lib, "fms_attention_decode_masked" if masked else
+              ("fms_attention_decode" if sink is None else "fms_attention_decode_sink"), *common, batch.n_seqs,
               n_splits, _ptr(part_o), _ptr(part_ml), nheads,
               kvheads, head_dim, float(scale), int(window), view.keys.shape[0], view.table.shape[0],
               int(getattr(batch, "total_len", 0)),
@@ -626,8 +669,9 @@ def attention(q: torch.Tensor, batch, view, nheads: int, kvheads: int, head_dim:
             launches += 1  # the kernel that merges the splits
     else:
         tiles = batch.query_tiles(tile_rows)
-        tail = () if sink is None else (_ptr(sink),)
-        _call(lib, "fms_attention_prefill" if sink is None else "fms_attention_prefill_sink", *common, _ptr(tiles),
+        tail = (_ptr(sink), int(chunk), float(softcap)) if masked else (() if sink is None else (_ptr(sink),))
+        _call(lib, "fms_attention_prefill_masked" if masked else
+              ("fms_attention_prefill" if sink is None else "fms_attention_prefill_sink"), *common, _ptr(tiles),
               tiles.shape[0], nheads, kvheads, head_dim, float(scale), int(window), view.keys.shape[0],
               view.table.shape[0], _ptr(error_flag(q.device)), *tail, _stream())
     return out
@@ -720,23 +764,34 @@ def selective_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_offset: int, dt_bia
     return y
 
 
-def delta_rule_scan(qkv: torch.Tensor, proj: torch.Tensor, beta_offset: int, a_raw: torch.Tensor, dt_bias: torch.Tensor,
-                    a_log: torch.Tensor, state: torch.Tensor, batch, heads: int, kvheads: int, dim: int, vdim: int,
-                    writes_state: bool = True) -> torch.Tensor:
+def delta_rule_scan(qkv: torch.Tensor, proj: torch.Tensor, beta_offset: int, a_raw: Optional[torch.Tensor],
+                    dt_bias: torch.Tensor, a_log: torch.Tensor, state: torch.Tensor, batch, heads: int, kvheads: int,
+                    dim: int, vdim: int, writes_state: bool = True, decay_offset: Optional[int] = None) -> torch.Tensor:
     """Per head, S = diag(g) S; u = beta (v - S^T k); S += k u^T; o = S^T q over each sequence's rows.  ``qkv`` float32
     [tokens, 2 kvheads * dim + heads * vdim] = [q | k | v]; beta = sigmoid(proj[:, beta_offset + head]);
     g = exp(-exp(a_log[head]) softplus(a_raw + dt_bias)), [heads * dim] a row; ``state`` float32 [slots, heads, vdim, dim].
-    q and k of ``qkv`` are made unit vectors in place on the way.  Returns o float32 [tokens, heads * vdim]."""
+    q and k of ``qkv`` are made unit vectors in place on the way.  Returns o float32 [tokens, heads * vdim].
+    ``decay_offset`` (with ``a_raw`` None): one decay a head instead of one a key channel,
+    g = exp(-exp(a_log[head]) softplus(proj[:, decay_offset + head] + dt_bias[head])), dt_bias [heads]."""
     n = qkv.shape[0]
+    per_head = decay_offset is not None
     if qkv.dtype != torch.float32 or state.dtype != torch.float32 or qkv.shape[1] != 2 * kvheads * dim + heads * vdim \
-            or tuple(state.shape[1:]) != (heads, vdim, dim) or tuple(a_raw.shape) != (n, heads * dim) \
-            or a_raw.dtype != proj.dtype:
+            or tuple(state.shape[1:]) != (heads, vdim, dim):
         raise KernelError("delta_rule_scan: qkv float32 [tokens, q | k | v], state float32 [slots, heads, vdim, dim]")
+    if per_head:
+        if a_raw is not None or dt_bias.shape[0] != heads or proj.shape[1] < decay_offset + heads:
+            raise KernelError("delta_rule_scan: one decay a head reads its logits from proj and a bias a head")
+        a_ptr, a_stride = _ptr(proj) + decay_offset * proj.element_size(), proj.shape[1]
+    else:
+        if tuple(a_raw.shape) != (n, heads * dim) or a_raw.dtype != proj.dtype or dt_bias.shape[0] != heads * dim:
+            raise KernelError("delta_rule_scan: decays' logits [tokens, heads * dim] in the projection's dtype")
+        a_ptr, a_stride = _ptr(a_raw), heads * dim
     o = torch.empty((n, heads * vdim), dtype=torch.float32, device=qkv.device)
     # decays [tokens, heads * dim], then betas [tokens, heads]
     scratch = torch.empty((n * heads * (dim + 1),), dtype=torch.float32, device=qkv.device)
     _call("state_scan", "fms_delta_rule_scan", _ptr(qkv), _ptr(proj) + beta_offset * proj.element_size(),
-          _code(proj.dtype), proj.shape[1], _ptr(a_raw), _ptr(dt_bias), _ptr(a_log), scratch.data_ptr(),
+          _code(proj.dtype), proj.shape[1], a_ptr, a_stride, 1 if per_head else 0, _ptr(dt_bias), _ptr(a_log),
+          scratch.data_ptr(),
           scratch.data_ptr() + 4 * n * heads * dim, _ptr(state), _ptr(o), _ptr(batch.first_row), _ptr(batch.slots), n,
           batch.n_seqs, heads, kvheads, dim, vdim, 1 if writes_state else 0, state.shape[0], _stream())
     global launches
@@ -792,7 +847,7 @@ def decay_scan(proj: torch.Tensor, state: torch.Tensor, batch, heads: int, dim: 
     return o
 
 
-GATE_NONE, GATE_SILU_BEFORE, GATE_SIGMOID_AFTER = 0, 1, 2
+GATE_NONE, GATE_SILU_BEFORE, GATE_SIGMOID_AFTER, GATE_SILU_AFTER = 0, 1, 2, 3
 
 
 def gated_group_rmsnorm(x: torch.Tensor, gate: Optional[torch.Tensor], gate_offset: int, gate_mode: int,
@@ -801,7 +856,7 @@ def gated_group_rmsnorm(x: torch.Tensor, gate: Optional[torch.Tensor], gate_offs
     """Rows of ``x`` (float32) cut into groups of ``group_size``, each divided by its root mean square, times
     ``weight`` (float32; repeated along the row where it is shorter), times ``factor``.  ``gate``: a matrix whose
     columns from ``gate_offset`` on are the gates' logits: ``GATE_SILU_BEFORE`` multiplies x by silu(gate) before the
-    norm, ``GATE_SIGMOID_AFTER`` the normed and weighted values by sigmoid(gate)."""
+    norm, ``GATE_SIGMOID_AFTER`` the normed and weighted values by sigmoid(gate), ``GATE_SILU_AFTER`` by silu(gate)."""
     n, width = x.shape
     if x.dtype != torch.float32 or weight.dtype != torch.float32 or width % weight.shape[0]:
         raise KernelError("gated_group_rmsnorm: x and weight are float32, the weight's length divides the row's")
@@ -844,17 +899,28 @@ class Routing:
     """What ``route`` leaves on the device: each pair's expert and weight, the experts' row ranges in the sorted
     matrix, and the sorted, weighted rows themselves."""
 
-    __slots__ = ("expert", "weight", "offsets", "tile_first", "row_of_pair", "group_of_row", "rows", "top", "experts")
+    __slots__ = ("expert", "weight", "offsets", "tile_first", "row_of_pair", "group_of_row", "rows", "top", "experts",
+                 "weights_on_output")
 
 
-def route(x: torch.Tensor, router: torch.Tensor, top: int) -> Routing:
-    """Scores sigmoid(x router^T) in float32; every token's ``top`` best experts; rows weight * x[token] sorted by
-    expert."""
+ROUTE_SIGMOID, ROUTE_SOFTMAX = 0, 1
+
+
+def route(x: torch.Tensor, router: torch.Tensor, top: int, mode: int = ROUTE_SIGMOID,
+          correction: Optional[torch.Tensor] = None, route_scale: float = 1.0) -> Routing:
+    """``ROUTE_SIGMOID``: scores sigmoid(x router^T) in float32; every token's ``top`` best experts; rows
+    weight * x[token] sorted by expert.  ``ROUTE_SOFTMAX``: scores softmax(x router^T) over all experts; the ``top``
+    experts with the largest score + ``correction`` [experts] (float32, or None) are the token's; its weights are their
+    scores over their sum (+ 1e-20), times ``route_scale``; the sorted rows are the tokens' as they are and
+    ``route_gather`` multiplies the experts' results by the weights."""
+    if correction is not None and (correction.dtype != torch.float32 or correction.shape[0] != router.shape[0]):
+        raise KernelError("route: the correction is float32, one number an expert")
     n, dim = x.shape
     experts = router.shape[0]
     dev = x.device
     r = Routing()
     r.top, r.experts = top, experts
+    r.weights_on_output = mode == ROUTE_SOFTMAX
     ints = torch.empty((n * top * 3 + 3 * (experts + 1),), dtype=torch.int32, device=dev)
     r.expert = ints[: n * top].view(n, top)
     r.row_of_pair = ints[n * top: 2 * n * top]
@@ -867,16 +933,17 @@ def route(x: torch.Tensor, router: torch.Tensor, top: int) -> Routing:
     r.rows = torch.empty((n * top, dim), dtype=x.dtype, device=dev)
     _call("grouped", "fms_route", _ptr(x), _code(x.dtype), _ptr(router), _code(router.dtype), _ptr(r.expert),
           _ptr(r.weight), _ptr(counts), _ptr(r.offsets), _ptr(r.tile_first), _ptr(r.row_of_pair), _ptr(r.group_of_row),
-          _ptr(r.rows), n, dim, experts, top, _stream())
+          _ptr(r.rows), n, dim, experts, top, int(mode), _ptr(correction), float(route_scale), _stream())
     global launches
     launches += 2
     return r
 
 
 def routed_linear(rows: torch.Tensor, weight: torch.Tensor, routing: Routing, glu: bool = False, limit: float = 0.0,
-                  alpha: float = 1.0) -> torch.Tensor:
+                  alpha: float = 1.0, relu_squared: bool = False) -> torch.Tensor:
     """Ragged groups: y[r] = rows[r] . weight[expert of r]^T; with ``glu`` weight[e] = [gate; up] and
-    y = g * sigmoid(alpha g) * (u + 1) for g = min(gate, limit), u = clamp(up, -limit, limit)."""
+    y = g * sigmoid(alpha g) * (u + 1) for g = min(gate, limit), u = clamp(up, -limit, limit); with ``relu_squared``
+    y = max(y, 0)^2."""
     n, k = rows.shape
     n_out = weight.shape[1] // (2 if glu else 1)
     if weight.dtype != rows.dtype or weight.shape[0] != routing.experts or weight.shape[2] != k:
@@ -887,6 +954,8 @@ def routed_linear(rows: torch.Tensor, weight: torch.Tensor, routing: Routing, gl
         # own kernels do), as the plain products of many rows take the library's; the gated unit is a kernel after it
         _ptr(rows), _ptr(weight)
         y = torch.nn.functional.grouped_mm(rows, weight.transpose(1, 2), offs=routing.offsets[1:])
+        if relu_squared and not glu:
+            _call("grouped", "fms_relu_squared", _ptr(y), _code(y.dtype), y.numel(), _stream())
         if not glu:
             return y
         out = torch.empty((n, n_out), dtype=rows.dtype, device=rows.device)
@@ -896,16 +965,17 @@ def routed_linear(rows: torch.Tensor, weight: torch.Tensor, routing: Routing, gl
     y = torch.empty((n, n_out), dtype=rows.dtype, device=rows.device)
     _call("grouped", "fms_grouped_linear", _ptr(rows), _ptr(weight), _ptr(y), _code(rows.dtype), _ptr(routing.offsets),
           _ptr(routing.tile_first), _ptr(routing.group_of_row), routing.experts, n, n_out, k, k, 0, n_out, 0,
-          1 if glu else 0, float(limit), float(alpha), 1 if n <= GROUPED_FEW_ROWS else 0, _stream())
+          1 if glu else (2 if relu_squared else 0), float(limit), float(alpha), 1 if n <= GROUPED_FEW_ROWS else 0, _stream())
     return y
 
 
 def route_gather(ys: torch.Tensor, routing: Routing) -> torch.Tensor:
-    """out[token] = the sum of its pairs' rows of ``ys``, float32, in the order of its choices."""
+    """out[token] = the sum of its pairs' rows of ``ys`` (each times its weight where the routing left the weights for
+    the experts' results), float32, in the order of its choices."""
     n = ys.shape[0] // routing.top
     out = torch.empty((n, ys.shape[1]), dtype=ys.dtype, device=ys.device)
     _call("grouped", "fms_route_gather", _ptr(ys), _code(ys.dtype), _ptr(routing.row_of_pair), _ptr(out), n, ys.shape[1],
-          routing.top, _stream())
+          routing.top, _ptr(routing.weight) if routing.weights_on_output else None, _stream())
     return out
 
 
@@ -915,10 +985,15 @@ USE_LATENT_MMA = os.environ.get("FMS_B200_LATENT_MMA", "1") != "0"  # 0: a promp
 
 
 def latent_prepare(proj: torch.Tensor, q_full: torch.Tensor, c_gain: torch.Tensor, eps: float, inv_freq: torch.Tensor,
-                   rot_dims: int, batch, view, heads: int, dim: int, rot: int, rank: int, writes_cache: bool = True) -> None:
+                   rot_dims: int, batch, view, heads: int, dim: int, rot: int, rank: int, writes_cache: bool = True,
+                   halves: bool = False, rot_mult: float = 1.0, kv: Optional[torch.Tensor] = None) -> None:
     """From the fused projection [q heads (dim + rot each) | c (rank) | kr (rot) | ...] of a step's rows: norms c,
     rotates kr and every head's rot part by the row's position, writes [c | kr] into the cache at the row's place and
-    the rotated query parts into q_full[:, h, rank:]."""
+    the rotated query parts into q_full[:, h, rank:].  ``kv``: [c | kr] are the first columns of this matrix instead
+    (queries that come from a projection of their own; ``proj`` then holds the query heads only).  ``halves``: value i
+    of a rotated run turns with value i + rot_dims / 2 instead of its neighbour; ``rot_mult`` multiplies sines and cosines."""
+    if kv is not None and (kv.dtype != proj.dtype or kv.shape[0] != proj.shape[0] or kv.shape[1] < rank + rot):
+        raise KernelError("latent_prepare: the latent's matrix has the projection's dtype and rows, and rank + rot columns")
     if view.keys.dtype != proj.dtype or q_full.dtype != proj.dtype:
         raise KernelError(f"cache is {view.keys.dtype}, activations are {proj.dtype}")
     _call("latent_attention", "fms_latent_prepare", _ptr(proj), _code(proj.dtype), proj.shape[1], _ptr(q_full), _ptr(c_gain),
@@ -926,14 +1001,28 @@ def latent_prepare(proj: torch.Tensor, q_full: torch.Tensor, c_gain: torch.Tenso
           _ptr(getattr(batch, "position_ids", None)), _ptr(batch.token_seq), _ptr(batch.slots), _ptr(view.keys),
           _ptr(view.table), view.table.shape[1], view.block_tokens, proj.shape[0], heads, dim, rot, rank,
           1 if writes_cache else 0, batch.slots.shape[0], view.table.shape[0], view.keys.shape[0],
-          _ptr(error_flag(proj.device)), _stream())
+          _ptr(error_flag(proj.device)), 1 if halves else 0, float(rot_mult), _ptr(kv), 0 if kv is None else kv.shape[1],
+          _stream())
+
+
+def latent_query_norm(proj: torch.Tensor, offset: int, n: int, gain: torch.Tensor, eps: float) -> torch.Tensor:
+    """Columns ``offset .. offset + n`` of ``proj``, each row divided by its root mean square over them, times ``gain``
+    [n]: the query's latent on its way to the projection that makes the heads' queries of it."""
+    if proj.shape[1] < offset + n or gain.shape[0] != n:
+        raise KernelError("latent_query_norm: the columns lie inside the rows and the gain has their number")
+    out = torch.empty((proj.shape[0], n), dtype=proj.dtype, device=proj.device)
+    _call("latent_attention", "fms_latent_query_norm", _ptr(proj) + offset * proj.element_size(), _code(proj.dtype),
+          proj.shape[1], n, _ptr(gain), _code(gain.dtype), float(eps), _ptr(out), proj.shape[0], _stream())
+    return out
 
 
 def latent_attention(q_full: torch.Tensor, batch, view, gate: Optional[torch.Tensor], gate_offset: int,
-                     sink: Optional[torch.Tensor], heads: int, rank: int, rot: int, scale: float) -> torch.Tensor:
+                     sink: Optional[torch.Tensor], heads: int, rank: int, rot: int, scale: float,
+                     window: int = 0) -> torch.Tensor:
     """Causal softmax attention of the step's rows over the cached latent rows [c | kr] (which already hold the step's
     own), with a per-head sink in the denominator and a per-head sigmoid gate on the result.  ``gate``: the matrix
-    whose column ``gate_offset + h`` holds head h's gate logit of each row.  Returns [tokens, heads, rank]."""
+    whose column ``gate_offset + h`` holds head h's gate logit of each row (None: no gate); ``sink`` None: no sink;
+    ``window`` > 0: the row at position p sees the keys p - window + 1 .. p only.  Returns [tokens, heads, rank]."""
     global _latent_split, launches
     n = q_full.shape[0]
     out = torch.empty((n, heads, rank), dtype=q_full.dtype, device=q_full.device)
@@ -962,7 +1051,7 @@ def latent_attention(q_full: torch.Tensor, batch, view, gate: Optional[torch.Ten
               _ptr(view.table), view.table.shape[1], view.block_tokens, _ptr(batch.slots), _ptr(batch.first_row),
               _ptr(batch.positions), _ptr(tiles), tiles.shape[0], tile_tokens, heads_per_block, heads, rank, rot,
               float(scale), batch.slots.shape[0], view.table.shape[0], view.keys.shape[0], _ptr(batch.token_seq), n_splits,
-              _ptr(part_o), _ptr(part_ml), _stream())
+              _ptr(part_o), _ptr(part_ml), int(window), _stream())
         if n_splits > 1:
             launches += 1
         return out
@@ -977,7 +1066,7 @@ def latent_attention(q_full: torch.Tensor, batch, view, gate: Optional[torch.Ten
           0 if gate is None else gate.shape[1], _ptr(sink), _code(sink.dtype) if sink is not None else F32,
           _ptr(view.table), view.table.shape[1], view.block_tokens, _ptr(batch.slots), _ptr(batch.token_seq),
           _ptr(batch.positions), n, n_splits, _ptr(part_o), _ptr(part_ml), heads, rank, rot, float(scale),
-          batch.slots.shape[0], view.table.shape[0], view.keys.shape[0], _stream())
+          batch.slots.shape[0], view.table.shape[0], view.keys.shape[0], int(window), _stream())
     if n_splits > 1:
         launches += 1
     return out

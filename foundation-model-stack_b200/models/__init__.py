@@ -137,6 +137,7 @@ from . import llama  # noqa: E402,F401  (registers the architecture and its vari
 from . import goletar  # noqa: E402,F401
 from . import niletar  # noqa: E402,F401
 from . import figonex  # noqa: E402,F401
+from . import giganex  # noqa: E402,F401
 
 
 def _import_plugins() -> None:

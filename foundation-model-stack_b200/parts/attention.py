@@ -83,6 +83,12 @@ class SinkAttention(Part):
             with ``gate`` "head" one a head
         values of another size than keys (``vdim``); ``values`` "keys": no value projection, a value is its key as
             projected, before norm and rotation
+        keys seen in runs (``chunk`` = n: the positions of a sequence are cut into runs of n, counted from its position 0,
+            and a query sees the keys of its own run up to itself; instead of a window)
+        capped scores (``softcap`` = c: s becomes c * tanh(s / c) after the scale)
+        a bias on the output projection (``out_bias``)
+        frequencies stretched by a ramp ("yarn" scaling of ``position``): the sines and cosines are then also multiplied
+            by the constant that belongs to it
 
     [Wq; Wk; Wv; Wg] is one fused projection (``in_proj``; bias [bq; bk; bv; 0] where ``bias``; without Wv where the
     values are the keys; its rows filled up with zeros to a multiple of 8 where the gates are one a head).  The cache holds heads
@@ -120,6 +126,10 @@ class SinkAttention(Part):
         self.out_factor = float(o.get("out_factor", 1.0))
         self.scale = 1.0 / math.sqrt(spec.head_dim) if spec.scale is None else float(spec.scale)
         self.window = int(spec.window)
+        self.chunk, self.softcap = int(o.get("chunk", 0)), float(o.get("softcap", 0.0))
+        if self.chunk < 0 or self.softcap < 0 or (self.chunk and self.window):
+            raise ValueError(f"sink_attention: chunk {self.chunk}, window {self.window}, softcap {self.softcap}")
+        self.rot_mult = 1.0
         self.position_spec = spec.position
         self.gate_col = (self.nheads + self.kvheads) * self.head_dim + (0 if self.values_are_keys else self.kvheads * self.vdim)
         rows = self.fused_rows(self.nheads, self.kvheads, self.head_dim, self.vdim, self.values_are_keys,
@@ -130,7 +140,7 @@ class SinkAttention(Part):
         if self.norm_first:
             self.declare("q_norm", (self.head_dim,), role="vector")
             self.declare("k_norm", (self.head_dim,), role="vector")
-        self.dense = self.add("dense", Linear(self.nheads * self.vdim, spec.dim, False))
+        self.dense = self.add("dense", Linear(self.nheads * self.vdim, spec.dim, bool(o.get("out_bias", False))))
         self._inv_freq = self._sink = self._q_gain = self._k_gain = None
 
     @staticmethod
@@ -144,12 +154,13 @@ class SinkAttention(Part):
     def finalize(self, device, dtype) -> None:
         super().finalize(device, dtype)
         if self.rot_dims:
-            from .position import rotary_inverse_frequencies
+            from .position import rotary_inverse_frequencies, rotary_multiplier
 
             # every frequency in float64, rounded to float32 once
             f = rotary_inverse_frequencies(self.rot_dims, float(self.position_spec.theta), self.position_spec.scaling_dict(),
                                            dtype=torch.float64)
             self._inv_freq = f.to(torch.float32).to(device).contiguous()
+            self.rot_mult = rotary_multiplier(self.position_spec.scaling_dict())
         if self.has_sink:
             self._sink = self.tensor("sink").float().contiguous()
         elif self.sink_logit is not None:
@@ -167,8 +178,9 @@ class SinkAttention(Part):
         q = ops.qk_prepare_store(proj, self._inv_freq, self.rot_dims, self.qk_norm, self.eps, batch, cache_view,
                                  self.nheads, self.kvheads, self.head_dim, self.vdim, self.pad, writes_cache,
                                  norm_first=self.norm_first, q_gain=self._q_gain, k_gain=self._k_gain, halves=self.halves,
-                                 values_are_keys=self.values_are_keys)
-        o = ops.attention(q, batch, cache_view, self.nheads, self.kvheads, self.pad, self.scale, self.window, self._sink)
+                                 values_are_keys=self.values_are_keys, rot_mult=self.rot_mult)
+        o = ops.attention(q, batch, cache_view, self.nheads, self.kvheads, self.pad, self.scale, self.window, self._sink,
+                          chunk=self.chunk, softcap=self.softcap)
         return ops.sigmoid_gate(o, proj if self.has_gate else None, self.gate_col, self.nheads, self.vdim, self.pad,
                                 self.out_factor, self.gate_per_head)
 

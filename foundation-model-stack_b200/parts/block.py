@@ -20,6 +20,9 @@ x += post2(feed_forward(pre2(x))).  What it hands on as pending is a ``NormedDel
 next layer's or the decoder's last) norms it, adds it and takes its own norm in one kernel.  A layer without a
 feed-forward ends after its mixer.
 
+``ParallelResidualBlock`` ("parallel_residual"): x += mixer(norm1(x)) + feed_forward(norm2(x)), both norms of the same
+stream and from one kernel; what it hands on is the list of its outputs with their factors.
+
 ``OutputNormBlock`` ("output_norm"): a norm on each sublayer's output only, x += norm1(mixer(x));
 x += norm2(feed_forward(x)); the sublayers read the stream itself.  What it hands on is a ``NormedDelta`` as well; the
 kernel that adds it also leaves the summed stream in the compute dtype for the sublayer that reads it next.
@@ -173,7 +176,46 @@ class OutputNormBlock(Part):
         return super().kernel_libraries(dtype) + ["elementwise"]
 
 
+class ParallelResidualBlock(Part):
+    """``parallel_residual``: both sublayers read the same stream, each through a norm of its own, and their outputs are
+    added together: x += mixer(norm1(x)) + feed_forward(norm2(x)).  The two norms come from one kernel
+    (``apply_pair``), which first adds what the layer before left pending; what this layer hands on is the list of its
+    outputs with their factors (``ScaledParts``: a mixer made of two gives two), added in float32 by whichever norm
+    comes next.  A layer without a feed-forward is x += mixer(norm1(x))."""
+
+    def __init__(self, spec: BlockSpec) -> None:
+        super().__init__()
+        n_mixer_norm, n_mixer, n_ff_norm, n_ff = spec.names
+        self.mixer_norm = self.add(n_mixer_norm, build_norm(spec.mixer_norm))
+        self.mixer = self.add(n_mixer, build_mixer(spec.mixer))
+        self.feed_forward = None
+        if spec.feed_forward is not None:
+            if spec.feed_forward_norm is None:
+                raise ValueError("a layer with a feed-forward needs its norm")
+            self.feed_forward_norm = self.add(n_ff_norm, build_norm(spec.feed_forward_norm))
+            self.feed_forward = self.add(n_ff, build_feed_forward(spec.feed_forward))
+        if not hasattr(self.mixer_norm, "apply_pair"):
+            raise ValueError("a parallel_residual layer needs norms with apply_pair (group_rmsnorm)")
+
+    def cache_request(self):
+        return self.mixer.cache_request()
+
+    def forward(self, residual, pending, batch, cache_view, writes_cache, dtype):
+        if self.feed_forward is None:
+            h = self.mixer_norm.apply(residual, pending, dtype)
+            a = self.mixer.forward(h, batch, cache_view, writes_cache)
+            return a if isinstance(a, ScaledParts) else ScaledParts([(a, 1.0)])
+        h1, h2 = self.mixer_norm.apply_pair(residual, pending, self.feed_forward_norm, dtype)
+        a = self.mixer.forward(h1, batch, cache_view, writes_cache)
+        parts = list(a.parts) if isinstance(a, ScaledParts) else [(a, 1.0)]
+        return ScaledParts(parts + [(self.feed_forward.forward(h2), 1.0)])
+
+    def kernel_libraries(self, dtype):
+        return super().kernel_libraries(dtype) + ["elementwise"]
+
+
 Block = PreNormBlock  # the name under which earlier callers know it
+register_block("parallel_residual", ParallelResidualBlock)
 register_block("output_norm", OutputNormBlock)
 register_block("post_norm", PostNormBlock)
 register_block("pre_norm", PreNormBlock)

@@ -19,6 +19,10 @@ d = post_norm(delta); residual += d; out = norm(residual), all float32.
 without dimensions in the checkpoint).  The number is read once when the weights are loaded and handed to the kernel
 by value.
 
+``GroupRMSNorm`` ("group_rmsnorm"): the row in equal consecutive runs, each by its own root mean square, the whole times
+the weight; adds several pending outputs with a factor each; ``apply_pair`` gives two norms of the same stream from
+one kernel.
+
 ``LayerNorm`` ("layernorm"): y = (x - mean(x)) / sqrt(mean((x - mean(x))^2) + eps) * w, no bias.  Option
 ``layer_scale``: a second vector ``scale`` multiplies the result element by element (the gain the kernel sees is
 w * scale, taken in float32 once).  It norms a sublayer's output on its way into the stream (as the ``norm`` of a
@@ -169,6 +173,50 @@ class LayerNorm(Part):
         return ["elementwise"]
 
 
+class GroupRMSNorm(Part):
+    """``group_rmsnorm``: the row is cut into ``groups`` equal consecutive runs (option; 1 by default), each divided by
+    its own root mean square (eps inside the root), and the whole multiplied by the weight.  What is pending may be a
+    tensor or several outputs with a factor each (an object with ``parts``: [(delta, factor), ...]); the norm adds them
+    to the stream in float32 in the pass that norms it.  ``apply_pair`` norms the same stream with this norm and a
+    second one of the same kind in one kernel (layers whose sublayers read the same stream side by side)."""
+
+    def __init__(self, spec: NormSpec) -> None:
+        super().__init__()
+        self.dim = spec.dim
+        self.eps = float(spec.eps)
+        self.groups = int(dict(spec.options).get("groups", 1))
+        if self.groups <= 0 or self.dim % self.groups:
+            raise ValueError(f"group_rmsnorm: a row of {self.dim} values in {self.groups} runs")
+        self.declare("weight", (spec.dim,), role="vector")
+        self._gain = None
+
+    def finalize(self, device, dtype) -> None:
+        super().finalize(device, dtype)
+        self._gain = self.tensor("weight").float().contiguous()
+
+    @staticmethod
+    def _parts(delta):
+        if delta is None or isinstance(delta, StreamCopy):
+            return []
+        if isinstance(delta, NormedDelta):
+            raise ValueError("group_rmsnorm adds plain outputs, not one that is normed on its way")
+        return list(delta.parts) if hasattr(delta, "parts") else [(delta, 1.0)]
+
+    def apply(self, residual, delta, out_dtype, rows=None):
+        return ops.parts_group_rmsnorm(residual, self._parts(delta), [self._gain], self.eps, self.groups, out_dtype, rows)[0]
+
+    def apply_pair(self, residual, delta, other: "GroupRMSNorm", out_dtype):
+        """(this norm of the stream, ``other``'s norm of it), after what is pending has been added."""
+        if not isinstance(other, GroupRMSNorm) or (other.eps, other.groups, other.dim) != (self.eps, self.groups, self.dim):
+            raise ValueError("apply_pair: two group_rmsnorm norms with the same runs and eps")
+        out = ops.parts_group_rmsnorm(residual, self._parts(delta), [self._gain, other._gain], self.eps, self.groups, out_dtype)
+        return out[0], out[1]
+
+    def kernel_libraries(self, dtype):
+        return ["elementwise"]
+
+
+register_norm("group_rmsnorm", GroupRMSNorm)
 register_norm("layernorm", LayerNorm)
 register_norm("rmsnorm", RMSNorm)
 register_norm("rmsnorm_scalar", ScalarRMSNorm)

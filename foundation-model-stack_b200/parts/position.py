@@ -20,7 +20,9 @@ fms/modules/positions.py:9-36, has ``adjusted_qk`` and ``adjusted_mask``):
 ``PositionEncoding`` is the base and encodes nothing.  ``RotaryEmbedding`` rotates adjacent pairs (2i, 2i+1) of
 every head by the angle position * inv_f[i], inv_f[i] = 1 / theta^(2i / head_dim), all in float32
 (fms/modules/positions.py:124-132 for the frequencies, :438-456 for the rotation); "llama3" rescales the
-frequencies as fms/modules/positions.py:171-196 does.  The reference keeps a table of cos/sin per position; here
+frequencies as fms/modules/positions.py:171-196 does; "yarn" (``rotary_inverse_frequencies``) stretches them by a
+ramp over the pair index and comes with a constant on sines and cosines (``rotary_multiplier``), which the mixers that
+know it hand to their kernels.  The reference keeps a table of cos/sin per position; here
 the kernel that writes keys into the cache computes them from the frequency vector, so no table exists and no
 length limit comes from it.
 """
@@ -56,7 +58,27 @@ def rotary_inverse_frequencies(head_dim: int, theta: float, scaling: dict, dtype
         blended = (1 - smooth) * slowed / factor + smooth * slowed
         medium = ~(wavelen < old / high) * ~(wavelen > old / low)
         return torch.where(medium, blended, slowed)
-    raise ValueError(f"rope scaling {kind!r} is not supported (supported: regular, linear, llama3)")
+    if kind == "yarn":
+        # frequencies between two wavelengths are stretched by a ramp over the pair index: pair i below ``lo`` keeps its
+        # frequency, above ``hi`` it is divided by ``factor``; lo and hi are the pairs whose waves make ``fast`` and
+        # ``slow`` turns over the ``original`` length
+        factor, original = float(scaling["factor"]), float(scaling["original"])
+        dims = 2 * inv.shape[0]
+
+        def pair_of(turns: float) -> float:
+            return dims * math.log(original / (2 * math.pi * turns)) / (2 * math.log(theta))
+
+        lo = max(math.floor(pair_of(float(scaling["fast"]))), 0)
+        hi = min(math.ceil(pair_of(float(scaling["slow"]))), dims - 1)
+        ramp = ((torch.arange(inv.shape[0]).to(dtype) - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+        return inv / factor * ramp + inv * (1 - ramp)
+    raise ValueError(f"rope scaling {kind!r} is not supported (supported: regular, linear, llama3, yarn)")
+
+
+def rotary_multiplier(scaling: dict) -> float:
+    """The constant that multiplies a rotation's sines and cosines: 0.1 ln(factor) + 1 with "yarn" scaling, else 1."""
+    kind = scaling.get("rope_type", scaling.get("type", "regular")) if scaling else "regular"
+    return 0.1 * math.log(float(scaling["factor"])) + 1.0 if kind == "yarn" else 1.0
 
 
 class PositionEncoding(Part):

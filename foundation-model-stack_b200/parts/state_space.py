@@ -20,6 +20,10 @@ mixer's input, H heads of ``vdim`` values (inner = H * vdim), a state of ``state
     S = diag(g) S;  u = beta (v - S^T k);  S = S + k u^T;  o = S^T q         (the read-out sees the token's own write)
     out = Wo (o / rms(o) * w * sigmoid(Wg2 (Wg1 h)))       rms per head over vdim, w [vdim] shared by the heads
 
+Option ``decay`` "head": one decay a head instead of one a key channel, g = exp(-exp(A_log_h) softplus(Wa h + dt_bias_h))
+with Wa [heads, width], and the gate is silu(Wg h) with Wg [heads * vdim, width] (no low-rank pairs); everything that
+reads h is then ONE projection [q; k; v; b; a; zeros up to a multiple of 8 rows; g].
+
 Projections that read h are fused into one matrix ([q; k; v; b] here, the checkpoint's one matrix there); the two
 low-rank pairs keep their first factors as products of their own, whose results the second factors read as they lie.
 Per sequence the cache holds the state matrices in float32 ([heads, vdim, rows], the rows contiguous) and the
@@ -103,24 +107,37 @@ class GatedDeltaRule(Part):
         o = dict(spec.options)
         self.heads, self.kvheads, self.head_dim = int(spec.nheads), int(spec.kvheads), int(spec.head_dim)
         self.vdim, self.taps, self.eps = int(o["vdim"]), int(o["conv"]), float(o["eps"])
-        self.decay_rank, self.gate_rank = int(o["decay_rank"]), int(o["gate_rank"])
+        self.per_head = o.get("decay", "channel") == "head"
+        if o.get("decay", "channel") not in ("channel", "head"):
+            raise ValueError(f"gated_delta_rule: decay {o.get('decay')!r}; known: channel, head")
+        self.decay_rank, self.gate_rank = (1, 1) if self.per_head else (int(o["decay_rank"]), int(o["gate_rank"]))
         self.out_factor = float(o.get("out_factor", 1.0))
         if min(self.heads, self.kvheads, self.head_dim, self.vdim, self.taps, self.decay_rank, self.gate_rank) <= 0 \
                 or self.heads % self.kvheads:
             raise ValueError(f"gated_delta_rule: {self.heads} heads of {self.vdim} over {self.kvheads} of {self.head_dim}, "
                              f"{self.taps} taps, ranks {self.decay_rank} and {self.gate_rank}")
         self.channels = 2 * self.kvheads * self.head_dim + self.heads * self.vdim
-        self.in_proj = self.add("in_proj", Linear(spec.dim, self.channels + self.heads, False))  # [q; k; v; b]
-        self.decay_in = self.add("decay_in", Linear(spec.dim, self.decay_rank, False))
-        self.decay_out = self.add("decay_out", Linear(self.decay_rank, self.heads * self.head_dim, False))
-        self.gate_in = self.add("gate_in", Linear(spec.dim, self.gate_rank, False))
-        self.gate_out = self.add("gate_out", Linear(self.gate_rank, self.heads * self.vdim, False))
+        if self.per_head:
+            self.gate_col = self.gate_column(self.kvheads, self.head_dim, self.heads, self.vdim)
+            self.in_proj = self.add("in_proj", Linear(spec.dim, self.gate_col + self.heads * self.vdim, False))
+        else:
+            self.in_proj = self.add("in_proj", Linear(spec.dim, self.channels + self.heads, False))  # [q; k; v; b]
+            self.decay_in = self.add("decay_in", Linear(spec.dim, self.decay_rank, False))
+            self.decay_out = self.add("decay_out", Linear(self.decay_rank, self.heads * self.head_dim, False))
+            self.gate_in = self.add("gate_in", Linear(spec.dim, self.gate_rank, False))
+            self.gate_out = self.add("gate_out", Linear(self.gate_rank, self.heads * self.vdim, False))
         self.declare("conv", (self.channels, self.taps), role="vector")
-        self.declare("dt_bias", (self.heads * self.head_dim,), role="vector")
+        self.declare("dt_bias", (self.heads if self.per_head else self.heads * self.head_dim,), role="vector")
         self.declare("A_log", (self.heads,), role="vector")
         self.declare("norm", (self.vdim,), role="vector")
         self.dense = self.add("dense", Linear(self.heads * self.vdim, spec.dim, False))
         self._f32 = {}
+
+    @staticmethod
+    def gate_column(kvheads: int, head_dim: int, heads: int, vdim: int) -> int:
+        """With one decay a head: the row of the fused projection [q; k; v; b; a; zeros; g] at which the gates begin (a
+        multiple of 8, so that their rows are read four at a time): what a checkpoint adapter has to put together."""
+        return (2 * kvheads * head_dim + heads * vdim + 2 * heads + 7) // 8 * 8
 
     def finalize(self, device, dtype) -> None:
         super().finalize(device, dtype)
@@ -136,6 +153,12 @@ class GatedDeltaRule(Part):
         p = self._f32
         proj = self.in_proj.forward(x)
         qkv = ops.causal_conv(proj, 0, self.channels, p["conv"], None, tail.state, batch, True, writes_cache)
+        if self.per_head:
+            o = ops.delta_rule_scan(qkv, proj, self.channels, None, p["dt_bias"], p["A_log"], matrix.state, batch, self.heads,
+                                    self.kvheads, self.head_dim, self.vdim, writes_cache,
+                                    decay_offset=self.channels + self.heads)
+            return ops.gated_group_rmsnorm(o, proj, self.gate_col, ops.GATE_SILU_AFTER, p["norm"], self.eps, self.vdim,
+                                           proj.dtype, self.out_factor)
         a = self.decay_out.forward(self.decay_in.forward(x))
         o = ops.delta_rule_scan(qkv, proj, self.channels, a, p["dt_bias"], p["A_log"], matrix.state, batch, self.heads,
                                 self.kvheads, self.head_dim, self.vdim, writes_cache)
