@@ -870,6 +870,143 @@ def run_reference(args):
     }))
 
 
+# --------------------------------------------------------------------------------------------------
+# --compare giganex: the Giganex design beside Llama at equal width, layer for layer
+# --------------------------------------------------------------------------------------------------
+GIGANEX_SHAPE = dict(width=4096, vocab=128256, groups=8, ff=14336, experts=16, top=4, expert_ff=3584,
+                     heads=32, kv_heads=8, dim=128, rot_dims=128, chunk=8192, softcap=30.0,
+                     delta_heads=16, delta_kv_heads=16, delta_dim=128, delta_vdim=128, conv=4,
+                     latent_heads=32, latent_dim=96, latent_rot=32, latent_vdim=128, q_rank=1536, kv_rank=512, window=4096)
+_GIGANEX_STRETCH = {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}
+
+
+def giganex_layers(kinds, mlps):
+    """`kinds`: the mixers ("parallel", "latent_attention", "attention"), `mlps`: their feed-forwards ("dense", "moe", None)."""
+    from fms_b200.models.giganex import (attention_layer, capped_side, delta_side, dense_mlp, latent_layer, moe_mlp,
+                                         parallel_layer, rotation)
+
+    g = GIGANEX_SHAPE
+    out = []
+    for kind, which in zip(kinds, mlps):
+        mlp = None if which is None else (dense_mlp(g["ff"]) if which == "dense" else moe_mlp(g["experts"], g["top"], g["expert_ff"], 2.0))
+        if kind == "parallel":
+            out.append(parallel_layer(capped_side(g["heads"], g["kv_heads"], g["dim"], g["dim"], g["dim"] ** -0.5, g["softcap"]),
+                                      delta_side(g["delta_heads"], g["delta_kv_heads"], g["delta_dim"], g["delta_vdim"], g["conv"]),
+                                      0.5, 0.5, mlp))
+        elif kind == "latent_attention":
+            out.append(latent_layer(g["latent_heads"], g["latent_dim"], g["latent_rot"], g["latent_vdim"], g["q_rank"], g["kv_rank"],
+                                    10000.0, _GIGANEX_STRETCH, (g["latent_dim"] + g["latent_rot"]) ** -0.5, g["window"], mlp))
+        else:
+            out.append(attention_layer(g["heads"], g["kv_heads"], g["dim"], g["dim"], rotation(g["rot_dims"], 500000.0, _GIGANEX_STRETCH),
+                                       g["dim"] ** -0.5, g["chunk"], mlp))
+    return out
+
+
+def giganex_counts(layers, tokens, batch_context, batch):
+    """(flops of a prompt of `tokens`, bytes a decode step of `batch` sequences with `batch_context` cached tokens
+    reads and writes) of the given layers: products, attention over the cache (keys and values, or latents), the delta
+    rule (8 flops per state value and token, float32 on the CUDA cores; its states read and written once a step), the
+    experts each token uses (for a decode step: the distinct experts that `batch` tokens are expected to hit)."""
+    g = GIGANEX_SHAPE
+    d, flops, moved = g["width"], 0.0, 0.0
+    for layer in layers:
+        m = layer["mixer"]
+        if layer["type"] == "attention":
+            w = d * (m["heads"] * m["dim"] + m["kv_heads"] * (m["dim"] + m["vdim"])) + m["heads"] * m["vdim"] * d
+            flops += tokens * tokens * m["heads"] * (m["dim"] + m["vdim"])  # the causal half of 2 T^2 (dim + vdim) a head
+            moved += 2 * batch_context * m["kv_heads"] * (m["dim"] + m["vdim"])
+        elif layer["type"] == "latent_attention":
+            h, dim, rot, v, qr, r = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["q_rank"], m["kv_rank"]
+            w = d * (qr + r + rot) + qr * h * (dim + rot) + h * dim * r + h * v * r + h * v * d
+            flops += tokens * tokens * h * (2 * r + rot)
+            moved += 2 * batch_context * (r + rot)
+        else:
+            l, r = m["left"], m["right"]
+            w = d * (l["heads"] * l["dim"] + l["kv_heads"] * (l["dim"] + l["vdim"]) + l["heads"] * l["vdim"]) + l["heads"] * l["vdim"] * d
+            flops += tokens * tokens * l["heads"] * (l["dim"] + l["vdim"])
+            moved += 2 * batch_context * l["kv_heads"] * (l["dim"] + l["vdim"])
+            w += d * (2 * r["kv_heads"] * r["dim"] + 2 * r["heads"] * r["vdim"] + 2 * r["heads"]) + r["heads"] * r["vdim"] * d
+            flops += 8.0 * tokens * r["heads"] * r["dim"] * r["vdim"]
+            moved += 2 * 4 * batch * r["heads"] * r["dim"] * r["vdim"]
+        flops += 2.0 * tokens * w
+        moved += 2 * w
+        mlp = layer.get("mlp")
+        if mlp and mlp["kind"] == "dense":
+            flops += 2.0 * tokens * 3 * mlp["ff"] * d
+            moved += 2 * 3 * mlp["ff"] * d
+        elif mlp:
+            e, top, f = mlp["router"]["experts"], mlp["router"]["top"], mlp["expert"]["ff"]
+            flops += 2.0 * tokens * (top * 2 * f * d + e * d)
+            hit = e * (1 - (1 - top / e) ** batch)
+            moved += 2 * (hit * 2 * f * d + e * d)
+    head = 2 * g["vocab"] * d
+    return flops + head, moved + head
+
+
+class GiganexMeasured(Measured):
+    """A Giganex model of given layers on the device, measured like the Llama one."""
+
+    def __init__(self, layers, room, max_prompt, slots):
+        import torch
+
+        from fms_b200.models.giganex import Giganex, GiganexConfig
+        from fms_b200.weights.sources import RandomSource
+
+        g = GIGANEX_SHAPE
+        self.m, self.dtype, self.nlayers, self.itemsize, self.layers = dict(vocab=g["vocab"]), "bf16", len(layers), 2, layers
+        self.model = Giganex(GiganexConfig(vocab=g["vocab"], width=g["width"], norm_groups=g["groups"], layers=layers))
+        self.model.load(RandomSource(self.model.checkpoint_layout(), 0, dtype=torch.bfloat16, device="cuda"), "native", "cuda",
+                        torch.bfloat16)
+        self.engine = self.model.new_engine(max_tokens=slots * (max_prompt + 2 * room + 128), max_slots=slots)
+        self.torch = torch
+
+
+def run_giganex(args):
+    """One JSON line: prompts of 512 and 2,048 tokens and decode steps of 1, 8 and 64 sequences, for `--layers` layers
+    (default 4) of the Giganex design at the width of the benchmark's Llama (the two mixers side by side with the dense
+    feed-forward of 14,336, attention over latents and attention over runs each with 16 experts of 3,584 of which a token
+    takes 4, taking turns), for as many Llama-3-8B layers, and for each of Giganex's mixers alone (models of one kind of
+    layer without a feed-forward) and the experts under one of them.  Each figure with its fraction of the measured
+    peak: flops of a prompt over the bf16 product peak, bytes a decode step moves over the copy peak."""
+    pk = peaks()
+    n = args.layers or 4
+    steps, warm = max(16, args.steps // 2), max(3, args.warmup // 2)
+    room = warm + 3 * steps + 8
+    lengths = {1: [1024], 8: [1024] * 8, 64: [1024] * 64}
+    out = {"compare": "giganex", "layers": n, "shape": GIGANEX_SHAPE, "peaks": pk, "steps": steps, "warmup": warm, "models": {}}
+
+    def measure(run, name, flops_bytes):
+        row = {}
+        for tokens in (512, 2048):
+            ms = run.prefill(tokens, 3)
+            row[f"prefill_{tokens}"] = {"ms": round(ms, 3), "tok_s": round(tokens / (ms / 1e3), 1),
+                                        "frac_of_bf16_peak": round(flops_bytes(tokens, 0, 0)[0] / (ms / 1e3) / 1e12 / pk["bf16_tflops"], 4)}
+        for b in (1, 8, 64):
+            v, ms, ctx, _, _ = run.device_decode(b, steps, warm, lengths[b], regions=3)
+            row[f"decode_b{b}"] = {"ms": round(ms, 4), "tok_s": round(v, 1),
+                                   "frac_of_copy_peak": round(flops_bytes(0, ctx, b)[1] / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 4)}
+        out["models"][name] = row
+        run.close()
+
+    order = [("parallel", "dense"), ("latent_attention", "moe"), ("attention", "moe")]
+    mixed = [order[i % 3] for i in range(n)]
+    variants = [("giganex", giganex_layers([k for k, _ in mixed], [f for _, f in mixed])),
+                ("parallel_only", giganex_layers(["parallel"] * n, [None] * n)),
+                ("latent_attention_only", giganex_layers(["latent_attention"] * n, [None] * n)),
+                ("attention_only", giganex_layers(["attention"] * n, [None] * n)),
+                ("attention_with_experts", giganex_layers(["attention"] * n, ["moe"] * n))]
+    if args.only:
+        variants = [v for v in variants if v[0] == args.only]
+    for name, layers in variants:
+        measure(GiganexMeasured(layers, room, 2048, 64), name,
+                lambda tokens, ctx, b, layers=layers: giganex_counts(layers, tokens, ctx, b))
+    if not args.only or args.only == "llama":
+        llama = Measured(MODEL, "bf16", n, room, 2048, slots=64)
+        measure(llama, "llama", lambda tokens, ctx, b: (prefill_flops(n, tokens), decode_bytes(n, ctx)))
+    print(json.dumps(out))
+
+
+# --------------------------------------------------------------------------------------------------
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--gpus", type=int, default=int(os.environ.get("WORLD_SIZE", "1")))
@@ -886,11 +1023,13 @@ def main():
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="with --only prefill: the prompt's length")
     ap.add_argument("--points", choices=["default", "main", "long"], default="default",
                     help="main: without the further configurations; long: also decode at batch 64 with 8k contexts")
-    ap.add_argument("--compare", choices=["", "goletar", "niletar", "figonex"], default="",
+    ap.add_argument("--compare", choices=["", "goletar", "niletar", "figonex", "giganex"], default="",
                     help="goletar: the Goletar design beside as many Llama layers of equal width (--layers, default 4; "
                     "--only goletar|mingru_only|latent_attention_only|mingru_with_experts|llama for one of them); "
                     "niletar: the Niletar design likewise (--only niletar|parallel_only|mamba2_only|llama); "
-                    "figonex: the Figonex design likewise (--only figonex|mlstm_only|attention_only|lightning_only|llama)")
+                    "figonex: the Figonex design likewise (--only figonex|mlstm_only|attention_only|lightning_only|llama); "
+                    "giganex: the Giganex design likewise (--only giganex|parallel_only|latent_attention_only|attention_only|"
+                    "attention_with_experts|llama)")
     args = ap.parse_args()
     choose_model(args.model)
     if args.gpus != 1:
@@ -903,6 +1042,8 @@ def main():
         run_niletar(args)
     elif args.compare == "figonex":
         run_figonex(args)
+    elif args.compare == "giganex":
+        run_giganex(args)
     elif args.impl == "reference":
         run_reference(args)
     elif args.only in ("gemm_rows", "attention_prefill", "attention_decode"):
