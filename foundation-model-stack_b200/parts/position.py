@@ -107,6 +107,11 @@ class RotaryEmbedding(PositionEncoding):
         super().__init__(spec)
         if spec.head_dim % 2:
             raise ValueError("rotary embedding needs an even head size")
+        if spec.scaling_dict().get("rope_type", spec.scaling_dict().get("type")) == "yarn":
+            # this part's fused kernels rotate by plain sines and cosines; the mixers that know the constant of such a
+            # scaling (sink_attention, latent_attention) take the frequencies themselves
+            raise ValueError("rope scaling 'yarn' comes with a constant on sines and cosines that this part's kernels do not "
+                             "take; sink_attention and latent_attention do")
         self._inv_freq_host = rotary_inverse_frequencies(spec.head_dim, spec.theta, spec.scaling_dict())
         self._inv_freq = None
 
