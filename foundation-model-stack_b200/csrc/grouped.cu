@@ -175,7 +175,31 @@ __global__ void __launch_bounds__(256) grouped_rows_kernel(const T* x, const T* 
   for (int r0 = r_lo; r0 < r_hi; r0 += 4) {
     const int nr = min(4, r_hi - r0);
     float a0[4] = {0.f, 0.f, 0.f, 0.f}, a1[4] = {0.f, 0.f, 0.f, 0.f};
-    if (vec) {
+    if (vec && !GLU) {
+      // two pieces of the row a lane and iteration (k and k + 256), both asked for before either is used: an ungated
+      // product has one row a warp, and one piece of it in flight does not cover the memory's latency
+      for (int k = lane * 8; k < K; k += 512) {
+        float wa[8], wb[8];
+        const bool two = k + 256 < K;
+        rows_load8(w0 + k, wa);
+        if (two) rows_load8(w0 + k + 256, wb);
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          if (i < nr) {
+            float xv[8], xw[8];
+            rows_load8(x + (size_t)(r0 + i) * x_row_stride + k, xv);
+            if (two) rows_load8(x + (size_t)(r0 + i) * x_row_stride + k + 256, xw);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) a0[i] = fmaf(xv[e], wa[e], a0[i]);
+            if (two) {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) a1[i] = fmaf(xw[e], wb[e], a1[i]);
+            }
+          }
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a0[i] += a1[i];
+    } else if (vec) {
       for (int k = lane * 8; k < K; k += 256) {
         float wa[8], wb[8];
         rows_load8(w0 + k, wa);

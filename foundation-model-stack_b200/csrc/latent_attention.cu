@@ -109,22 +109,51 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(
 }
 
 // A run of columns of a wider matrix, normed row by row: out[t, :n] = x[t, off : off + n] / sqrt(mean(.^2) + eps) * gain
-// (queries that go through a latent of their own).  A warp a row, four rows a block; float32 arithmetic.
+// (queries that go through a latent of their own).  A block a row; with `vec` (n and the row stride multiples of 4
+// values, the bases aligned to four values) a thread takes four values at a time; float32 arithmetic.
+template <typename T> __device__ __forceinline__ void qn_load4(const T* p, float* v);
+template <> __device__ __forceinline__ void qn_load4<float>(const float* p, float* v) {
+  const float4 t = *reinterpret_cast<const float4*>(p);
+  v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+template <> __device__ __forceinline__ void qn_load4<__nv_bfloat16>(const __nv_bfloat16* p, float* v) {
+  const uint2 t = *reinterpret_cast<const uint2*>(p);
+  v[0] = __uint_as_float(t.x << 16); v[1] = __uint_as_float(t.x & 0xffff0000u);
+  v[2] = __uint_as_float(t.y << 16); v[3] = __uint_as_float(t.y & 0xffff0000u);
+}
+
 template <typename T, typename TG>
 __global__ void __launch_bounds__(128) latent_query_norm_kernel(const T* x, int stride, int n, const TG* gain, float eps,
-                                                               T* out, int n_tokens) {
+                                                               T* out, int n_tokens, int vec) {
+  __shared__ float scratch[33];
   pdl_launch_dependents();
   pdl_wait();
-  const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  if (t >= n_tokens) return;
+  const int t = blockIdx.x;
   const T* row = x + (size_t)t * stride;
   float ss = 0.f;
-  for (int d = lane; d < n; d += 32) {
-    const float v = to_f32(row[d]);
-    ss += v * v;
+  if (vec) {
+    for (int d = threadIdx.x * 4; d < n; d += blockDim.x * 4) {
+      float v[4];
+      qn_load4<T>(row + d, v);
+      ss += (v[0] * v[0] + v[1] * v[1]) + (v[2] * v[2] + v[3] * v[3]);
+    }
+  } else {
+    for (int d = threadIdx.x; d < n; d += blockDim.x) {
+      const float v = to_f32(row[d]);
+      ss += v * v;
+    }
   }
-  const float inv = 1.f / sqrtf(warp_sum(ss) / (float)n + eps);
-  for (int d = lane; d < n; d += 32) out[(size_t)t * n + d] = from_f32<T>(to_f32(row[d]) * inv * to_f32(gain[d]));
+  const float inv = 1.f / sqrtf(block_sum(ss, scratch) / (float)n + eps);
+  if (vec) {
+    for (int d = threadIdx.x * 4; d < n; d += blockDim.x * 4) {
+      float v[4];
+      qn_load4<T>(row + d, v);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) out[(size_t)t * n + d + e] = from_f32<T>(v[e] * inv * to_f32(gain[d + e]));
+    }
+  } else {
+    for (int d = threadIdx.x; d < n; d += blockDim.x) out[(size_t)t * n + d] = from_f32<T>(to_f32(row[d]) * inv * to_f32(gain[d]));
+  }
 }
 
 struct LatentArgs {
@@ -548,9 +577,11 @@ FMS_API int fms_latent_query_norm(const void* x, int dtype, int stride, int n, c
                                   void* out, int n_tokens, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (n <= 0 || stride < n) return fms_fail("latent_query_norm: %d columns of rows of %d", n, stride);
+  const size_t item = dtype == FMS_BF16 ? 2 : 4;
+  const int vec = n % 4 == 0 && stride % 4 == 0 && (uintptr_t)x % (4 * item) == 0;
   FMS_DISPATCH_DTYPE(dtype, T, FMS_DISPATCH_DTYPE(gain_dtype, TG,
-                     fms_launch(latent_query_norm_kernel<T, TG>, dim3((n_tokens + 3) / 4), dim3(128), 0, stream, (const T*)x,
-                                stride, n, (const TG*)gain, eps, (T*)out, n_tokens)));
+                     fms_launch(latent_query_norm_kernel<T, TG>, dim3(n_tokens), dim3(128), 0, stream, (const T*)x,
+                                stride, n, (const TG*)gain, eps, (T*)out, n_tokens, vec)));
   return fms_launch_status("latent_query_norm");
 }
 
