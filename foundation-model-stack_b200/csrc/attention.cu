@@ -74,10 +74,14 @@ __device__ __forceinline__ int first_visible(const AttnArgs& a, int pos) {
   return 0;
 }
 
-// For kernels that fold the scale into the exponent: the raw dot product r replaced by r' with
-// r' * scale = softcap * tanh(r * scale / softcap).
+// For kernels that fold the scale into the exponent (the bfloat16 tensor-core kernels): the raw dot product r replaced
+// by r' with r' * scale = softcap * tanh(r * scale / softcap).  tanh(x) = 1 - 2 / (exp(2 x) + 1) with the fast
+// exponential and division: its absolute error is a few 1e-7 (times the cap: far below what rounding the
+// probabilities to bfloat16 costs), it saturates to +-1 without a case of its own, and it costs a third of tanhf,
+// which doubled the tcgen05 prefill kernel's time (120 against 62 us for 2,048 tokens of 32 heads).
 __device__ __forceinline__ float capped_raw(const AttnArgs& a, float raw) {
-  return tanhf(raw * (a.scale / a.softcap)) * (a.softcap / a.scale);
+  const float t = __expf(2.f * raw * (a.scale / a.softcap));
+  return (1.f - __fdividef(2.f, t + 1.f)) * (a.softcap / a.scale);
 }
 
 // The cache block that holds key block kb of the sequence in `slot`; negative: none (a block given back behind a

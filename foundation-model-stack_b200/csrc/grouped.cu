@@ -149,6 +149,12 @@ __device__ __forceinline__ void rows_load8(const __nv_bfloat16* p, float* v) {
   }
 }
 
+// pieces of a weight row that a lane of the row-walking kernel has in flight for an ungated product.  Measured through
+// decode steps of 8 sequences over four layers with 16 experts of 3,584: one piece 2.00 ms, two 1.67, four 2.85 (the
+// registers of four pieces and of their rows of x cost more blocks a multiprocessor than the loads in flight gain)
+#ifndef FMS_ROW_PIECES
+#define FMS_ROW_PIECES 2
+#endif
 // vec != 0: K, the strides and the group offsets are multiples of 8 values and the bases 16-byte aligned: a lane reads 8
 // values at a time
 template <typename T, bool GLU>
@@ -176,29 +182,37 @@ __global__ void __launch_bounds__(256) grouped_rows_kernel(const T* x, const T* 
     const int nr = min(4, r_hi - r0);
     float a0[4] = {0.f, 0.f, 0.f, 0.f}, a1[4] = {0.f, 0.f, 0.f, 0.f};
     if (vec && !GLU) {
-      // two pieces of the row a lane and iteration (k and k + 256), both asked for before either is used: an ungated
+      // PIECES pieces of the row a lane and iteration (k, k + 256, ...), all asked for before any is used: an ungated
       // product has one row a warp, and one piece of it in flight does not cover the memory's latency
-      for (int k = lane * 8; k < K; k += 512) {
-        float wa[8], wb[8];
-        const bool two = k + 256 < K;
-        rows_load8(w0 + k, wa);
-        if (two) rows_load8(w0 + k + 256, wb);
+      constexpr int PIECES = FMS_ROW_PIECES;
+      float part[PIECES][4];
+#pragma unroll
+      for (int p = 0; p < PIECES; ++p) part[p][0] = part[p][1] = part[p][2] = part[p][3] = 0.f;
+      for (int k = lane * 8; k < K; k += 256 * PIECES) {
+        float wv[PIECES][8];
+#pragma unroll
+        for (int p = 0; p < PIECES; ++p)
+          if (k + 256 * p < K) rows_load8(w0 + k + 256 * p, wv[p]);
 #pragma unroll
         for (int i = 0; i < 4; ++i)
           if (i < nr) {
-            float xv[8], xw[8];
-            rows_load8(x + (size_t)(r0 + i) * x_row_stride + k, xv);
-            if (two) rows_load8(x + (size_t)(r0 + i) * x_row_stride + k + 256, xw);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) a0[i] = fmaf(xv[e], wa[e], a0[i]);
-            if (two) {
+            for (int p = 0; p < PIECES; ++p)
+              if (k + 256 * p < K) {
+                float xv[8];
+                rows_load8(x + (size_t)(r0 + i) * x_row_stride + k + 256 * p, xv);
 #pragma unroll
-              for (int e = 0; e < 8; ++e) a1[i] = fmaf(xw[e], wb[e], a1[i]);
-            }
+                for (int e = 0; e < 8; ++e) part[p][i] = fmaf(xv[e], wv[p][e], part[p][i]);
+              }
           }
       }
 #pragma unroll
-      for (int i = 0; i < 4; ++i) a0[i] += a1[i];
+      for (int i = 0; i < 4; ++i) {
+        float sum = part[0][i];
+#pragma unroll
+        for (int p = 1; p < PIECES; ++p) sum += part[p][i];
+        a0[i] = sum;
+      }
     } else if (vec) {
       for (int k = lane * 8; k < K; k += 256) {
         float wa[8], wb[8];
