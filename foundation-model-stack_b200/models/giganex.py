@@ -153,15 +153,47 @@ class Giganex(Model):
         return {"architecture": "Giganex", "vocab": c.vocab, "width": c.width,
                 "norm": {"eps": c.norm_eps, "groups": c.norm_groups}, "layers": copy.deepcopy(c.layers)}
 
+    def load(self, source, adapter_source, device, dtype):
+        # a size that config.json leaves out is read from the checkpoint's shapes
+        shapes = {}
+
+        def rows(name, axis=0):
+            if name not in shapes:
+                shapes[name] = tuple(source.spec(name)[1]) if name in names else None
+            return None if shapes[name] is None else int(shapes[name][axis])
+
+        names = set(source.keys())
+        for i, layer in enumerate(self.config.layers):
+            p, m = f"l{i}.", layer["mixer"]
+            found = {}
+            if layer["type"] == "latent_attention":
+                found = {"q_rank": rows(p + "mix.dq"), "kv_rank": rows(p + "mix.dkv.norm")}
+                target = m
+            elif layer["type"] == "parallel":
+                found = {"conv": rows(p + "mix.right.q.conv", 1)}
+                target = m["right"]
+            for key, value in found.items():
+                if key not in target and value is not None:
+                    target[key] = value
+            mlp = layer.get("mlp")
+            if mlp is not None and mlp.get("kind") == "dense" and "ff" not in mlp and rows(p + "mlp.gate") is not None:
+                mlp["ff"] = rows(p + "mlp.gate")
+            if mlp is not None and mlp.get("kind") == "moe":
+                if "ff" not in mlp.setdefault("expert", {}) and rows(p + "mlp.e0.up") is not None:
+                    mlp["expert"]["ff"] = rows(p + "mlp.e0.up")
+                if "experts" not in mlp.setdefault("router", {}) and rows(p + "mlp.router") is not None:
+                    mlp["router"]["experts"] = rows(p + "mlp.router")
+        return super().load(source, adapter_source, device, dtype)
+
     # ---- specs -------------------------------------------------------------------------------
     def _mixer_spec(self, layer: dict) -> MixerSpec:
         c, m = self.config, layer["mixer"]
         eps = float(c.norm_eps)
         if layer["type"] == "attention":
             rot = m.get("rot") or {}
-            return MixerSpec("sink_attention", dim=c.width, nheads=int(m["heads"]), kvheads=int(m["kv_heads"]),
+            return MixerSpec("sink_attention", dim=c.width, nheads=int(m["heads"]), kvheads=int(m.get("kv_heads", m["heads"])),
                              head_dim=int(m["dim"]), bias=False, scale=float(m["scale"]), position=_position(rot),
-                             options=(("vdim", int(m["vdim"])), ("rot_dims", int(rot.get("dims", 0))), ("pairing", "halves"),
+                             options=(("vdim", int(m.get("vdim", m["dim"]))), ("rot_dims", int(rot.get("dims", 0))), ("pairing", "halves"),
                                       ("qk_norm", True), ("eps", eps), ("chunk", int((m.get("mask") or {}).get("size", 0)))))
         if layer["type"] == "latent_attention":
             rot = m.get("rot") or {}
@@ -171,11 +203,11 @@ class Giganex(Model):
                                       ("rot_dims", int(rot.get("dims", m["rot_dim"]))), ("eps", eps),
                                       ("q_rank", int(m["q_rank"])), ("sink", False), ("gate", False), ("pairing", "halves")))
         left, right = m["left"], m["right"]
-        left_spec = MixerSpec("sink_attention", dim=c.width, nheads=int(left["heads"]), kvheads=int(left["kv_heads"]),
+        left_spec = MixerSpec("sink_attention", dim=c.width, nheads=int(left["heads"]), kvheads=int(left.get("kv_heads", left["heads"])),
                               head_dim=int(left["dim"]), bias=True, scale=float(left["scale"]),
-                              options=(("vdim", int(left["vdim"])), ("gate", True), ("out_bias", True),
+                              options=(("vdim", int(left.get("vdim", left["dim"]))), ("gate", True), ("out_bias", True),
                                        ("softcap", float(left.get("softcap", 0.0)))))
-        right_spec = MixerSpec("gated_delta_rule", dim=c.width, nheads=int(right["heads"]), kvheads=int(right["kv_heads"]),
+        right_spec = MixerSpec("gated_delta_rule", dim=c.width, nheads=int(right["heads"]), kvheads=int(right.get("kv_heads", right["heads"])),
                                head_dim=int(right["dim"]),
                                options=(("vdim", int(right["vdim"])), ("conv", int(right["conv"])), ("eps", eps),
                                         ("decay", "head")))

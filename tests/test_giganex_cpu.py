@@ -85,6 +85,25 @@ def test_config_json_of_another_design_or_with_unknown_layers_is_refused():
         Giganex.config_from_json(bad)
 
 
+def test_sizes_that_config_json_leaves_out_come_from_the_shapes(tmp_path):
+    from fms_b200.models import get_model
+
+    cfg = json.loads(json.dumps(gm.CONFIGS["p"]))
+    weights = gm.tensors(cfg, 3)
+    del cfg["layers"][0]["mixer"]["q_rank"], cfg["layers"][0]["mixer"]["kv_rank"], cfg["layers"][1]["mixer"]["right"]["conv"]
+    del cfg["layers"][1]["mlp"]["ff"], cfg["layers"][0]["mlp"]["expert"]["ff"], cfg["layers"][0]["mlp"]["router"]["experts"]
+    del cfg["layers"][2]["mixer"]["kv_heads"]  # as many key heads as heads would be read; the checkpoint has one: refused
+    folder = gm.write_folder(str(tmp_path / "p"), cfg, weights)
+    from fms_b200.weights import WeightError
+
+    with pytest.raises(WeightError):
+        get_model("hf_pretrained", model_path=folder, device_type="cpu", data_type="fp32")
+    cfg["layers"][2]["mixer"]["kv_heads"] = 1
+    folder = gm.write_folder(str(tmp_path / "p2"), cfg, weights)
+    model = get_model("hf_pretrained", model_path=folder, device_type="cpu", data_type="fp32")
+    assert model.config_json() == gm.CONFIGS["p"]
+
+
 def test_random_weights_of_a_registered_variant():
     from fms_b200.models import get_model
 
