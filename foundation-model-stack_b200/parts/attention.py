@@ -181,6 +181,8 @@ class SinkAttention(Part):
                                  values_are_keys=self.values_are_keys, rot_mult=self.rot_mult)
         o = ops.attention(q, batch, cache_view, self.nheads, self.kvheads, self.pad, self.scale, self.window, self._sink,
                           chunk=self.chunk, softcap=self.softcap)
+        if not self.has_gate and self.pad == self.vdim and self.out_factor == 1.0:
+            return o  # no gate, no padding to drop, no factor: the heads' results as attention left them
         return ops.sigmoid_gate(o, proj if self.has_gate else None, self.gate_col, self.nheads, self.vdim, self.pad,
                                 self.out_factor, self.gate_per_head)
 
