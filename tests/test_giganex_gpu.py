@@ -4,6 +4,7 @@ into portions down to two tokens, unequal batches, slots, blocks and states that
 the edges of cache blocks, of the decode kernels' key splits, of runs and of windows, greedy generation and the trace
 program."""
 import json
+import math
 import os
 import subprocess
 import sys
@@ -194,6 +195,92 @@ def test_norm_in_runs_with_pending_parts(dtype, dim, groups):
         (o,) = ops.parts_group_rmsnorm(r, [(t.cuda(), f) for t, f in parts], [gains[0].cuda()], 1e-5, groups, dt, rows.cuda())
         assert torch.equal(r.cpu(), res)
         close(o, want[0][rows.long()], dtype, loose=0.5)
+
+
+def plain_masked_attention(q, batch, view, nheads, kvheads, hd, scale, chunk, softcap):
+    """The step's queries over the cache, row by row in float32: keys of the query's own run of ``chunk`` positions
+    (0: all earlier keys), scores capped by ``softcap`` (0: as they are)."""
+    import plain_ops as P
+
+    out = torch.zeros_like(q)
+    first, lens, slots = batch.first_row.tolist(), batch.len_after.tolist(), batch.slots.tolist()
+    group = nheads // kvheads
+    for i in range(batch.n_seqs):
+        n_new = first[i + 1] - first[i]
+        for j in range(n_new):
+            p = lens[i] - n_new + j
+            lo = p - p % chunk if chunk else 0
+            k, v = P.gather_cache(view, slots[i], lo, p + 1)
+            s = torch.einsum("hd,thd->ht", q[first[i] + j].float().view(nheads, hd), k.repeat_interleave(group, dim=1)) * scale
+            if softcap:
+                s = softcap * torch.tanh(s / softcap)
+            out[first[i] + j] = torch.einsum("ht,thd->hd", torch.softmax(s, -1), v.repeat_interleave(group, dim=1)).reshape(-1).to(q.dtype)
+    return out
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+@pytest.mark.parametrize("nheads,kvheads,hd,lens_before,num_new,chunk,softcap", [
+    (4, 2, 16, [0, 0, 0], [5, 70, 17], 16, 0.0),          # prompts from an empty cache, runs shorter than a block
+    (3, 1, 32, [100, 3, 64], [1, 1, 1], 64, 2.0),         # decode: a run that began at a block's edge, one that begins now
+    (5, 5, 48, [130, 0], [40, 129], 100, 1.0),            # continuation onto a cached prefix over a run's edge, capped
+    (12, 1, 64, [300], [1], 0, 0.5),                      # decode with 12 query heads on one kv head, cap alone
+    (2, 2, 128, [513], [1], 257, 0.0),                    # decode over three splits of which the run touches two
+    (8, 2, 128, [0, 100], [200, 77], 150, 3.0),           # prefill on the tcgen05 kernel, head size 128
+    (4, 4, 64, [64, 0], [130, 1], 64, 4.0),               # prefill, head size 64, runs of one block
+    (4, 2, 80, [10], [70], 33, 0.0),                      # prefill on mma.sync
+    (2, 1, 64, [33000], [1], 5000, 1.5),                  # decode over more splits than the merge stages in shared memory
+    (8, 8, 128, [33000, 100, 5000, 64], [1, 1, 1, 1], 4000, 2.5),  # enough to read for the streaming kernel
+])
+def test_attention_kernels_in_runs_and_with_a_cap(dtype, nheads, kvheads, hd, lens_before, num_new, chunk, softcap):
+    """The attention kernels themselves over a poisoned cache with scrambled blocks: every kernel (float32 and the
+    tensor-core ones for prompts, split keys and the streamed cache for decode steps) with runs, a cap, and both."""
+    from test_kernels_gpu import make_cache_case, tol
+
+    from fms_b200.kernels import ops
+
+    dt = DTYPES[dtype]
+    cache, view, batch = make_cache_case(dt, nheads, kvheads, hd, lens_before, num_new, 9)
+    g = torch.Generator().manual_seed(hd + chunk)
+    qkv = (torch.randn(sum(num_new), (nheads + 2 * kvheads) * hd, generator=g) * 1.5).to(dt).cuda()
+    q = ops.rope_store(qkv, None, batch, view, nheads, kvheads, hd)
+    scale = 1.0 / math.sqrt(hd)
+    want = plain_masked_attention(q, batch, view, nheads, kvheads, hd, scale, chunk, softcap)
+    got = ops.attention(q, batch, view, nheads, kvheads, hd, scale, 0, None, chunk=chunk, softcap=softcap)
+    ops.check_error_flag("cuda")
+    assert not torch.isnan(got).any()
+    torch.testing.assert_close(got.float(), want.float(), **tol(dt))
+
+
+def test_streamed_decode_attention_in_runs_with_a_cap():
+    """Seventy sequences of 32 heads over 8: decode attention is the persistent kernel that streams the cache by TMA;
+    with runs of 300 positions and a cap of 3, and one marked key inside the first sequence's run and one just before it."""
+    from test_kernels_gpu import make_cache_case, tol
+
+    from fms_b200.kernels import ops
+
+    dt, nheads, kvheads, hd, chunk, softcap = torch.bfloat16, 32, 8, 128, 300, 3.0
+    g = torch.Generator().manual_seed(23)
+    lens = [int(v) for v in torch.randint(1, 700, (70,), generator=g)]
+    lens[0], lens[1], lens[2] = 699, 256, 1
+    cache, view, batch = make_cache_case(dt, nheads, kvheads, hd, lens, [1] * 70, 16)
+    qkv = torch.randn(70, (nheads + 2 * kvheads) * hd, generator=g).to(dt).cuda()
+    q = ops.rope_store(qkv, None, batch, view, nheads, kvheads, hd)
+    table = cache.groups[0].table_host
+    head, group = nheads - 1, nheads // kvheads
+    for far, value in ((600, 2.0), (599, -5.0)):  # the query at position 699 sees 600..699
+        blk = int(table[int(batch.slots[0]), far // 64])
+        view.keys[blk, head // group, far % 64] = (q[0, head * hd:(head + 1) * hd].float() * 6).to(dt)
+        view.values[blk, head // group, far % 64] = torch.full((hd,), value).to(dt).cuda()
+    scale = 1.0 / math.sqrt(hd)
+    before = ops.attention_stream_launches(hd)
+    got = ops.attention(q, batch, view, nheads, kvheads, hd, scale, 0, None, chunk=chunk, softcap=softcap)
+    ops.check_error_flag("cuda")
+    assert ops.attention_stream_launches(hd) == before + 1  # it was this kernel that ran
+    want = plain_masked_attention(q, batch, view, nheads, kvheads, hd, scale, chunk, softcap)
+    assert not torch.isnan(got).any()
+    torch.testing.assert_close(got.float(), want.float(), **tol(dt))
+    # the cap bounds the marked key's score at 3, so it shares the weight with the run's other 99 keys instead of taking all
+    assert float(want[0, head * hd].float()) < 1.0 and float(got[0, head * hd].float()) < 1.0
 
 
 def chunked_tensors(g, dim_in, m):
