@@ -660,6 +660,39 @@ def test_unequal_batches_freed_slots_and_poisoned_blocks(folders, oracles, which
     engine.check()
 
 
+@pytest.mark.parametrize("seed", [0, 4, 5, 7, 12, 16])
+def test_configurations_drawn_at_random(seed, tmp_path):
+    """Layers of any kinds in any order with sizes drawn from a seed, float32: a prompt whole, its last 30 tokens one by
+    one, and three unequal requests started together and decoded together, every row against the oracle."""
+    from fms_b200.models import get_model
+
+    cfg = gm.random_config(seed)
+    weights = gm.tensors(cfg, 100 + seed, std=0.05)
+    folder = gm.write_folder(str(tmp_path / "m"), cfg, weights)
+    model = get_model("hf_pretrained", model_path=folder, device_type="cuda", data_type="fp32")
+    engine = model.new_engine(max_tokens=1024, max_slots=4, sampling=False)
+    reqs = [gm.prompt(cfg, n, seed + i) for i, n in enumerate((170, 37, 90))]
+    want = [pg.forward(cfg, weights, ids) for ids in reqs]
+    (slot,) = engine.begin(1)
+    close(engine.step([slot], [reqs[0]], [list(range(170))]), want[0], "fp32", loose=2)
+    engine.release([slot])
+    (slot,) = engine.begin(1)
+    got = [engine.step([slot], [reqs[0][:140]], [list(range(140))])] + [engine.step([slot], [[t]], [[0]]) for t in reqs[0][140:]]
+    close(torch.cat(got), want[0], "fp32", loose=2)
+    engine.release([slot])
+    slots = engine.begin(3)
+    first = engine.step(slots, [q[:-8] for q in reqs], [list(range(len(q) - 8)) for q in reqs])
+    outs = [[p] for p in torch.split(first, [len(q) - 8 for q in reqs])]
+    for t in range(8):
+        rows = engine.step(slots, [[q[len(q) - 8 + t]] for q in reqs])
+        for i in range(3):
+            outs[i].append(rows[i][None])
+    engine.release(slots)
+    for i in range(3):
+        close(torch.cat(outs[i]), want[i], "fp32", loose=2)
+    engine.check()
+
+
 def test_many_sequences_in_one_decode_step_fill_rows_and_graphs(folders, oracles):
     """Eleven sequences decode together (filled up to twelve rows with rows in the spare slot), then nine of them."""
     which, cfg, dtype = "p", gm.CONFIGS["p"], "fp32"
