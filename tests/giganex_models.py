@@ -101,14 +101,14 @@ def random_config(seed):
     def mlp():
         kind = r.choice(["dense", "moe", "moe", None])
         if kind == "dense":
-            return dense(r.choice([48, 100, 384]))
+            return dense(r.choice([48, 100, 360]))
         if kind == "moe":
             e = r.choice([4, 8, 16, 6])
-            return moe(e, r.choice([1, 2, 4, e]), r.choice([32, 96, 40]), r.choice([1.0, 1.5, 2.5]))
+            return moe(e, r.choice([1, 2, 4, e]), r.choice([32, 88, 40]), r.choice([1.0, 1.5, 2.5]))
         return None
 
     def scaling():
-        return r.choice([None, {"factor": r.choice([2.0, 8.0, 32.0]), "original": r.choice([64, 512, 2048]),
+        return r.choice([None, {"factor": r.choice([2.0, 8.0, 32.0]), "original": r.choice([64, 500, 3000]),
                                 "fast": r.choice([8.0, 32.0]), "slow": r.choice([1.0, 2.0])}])
 
     layers = []
@@ -117,18 +117,18 @@ def random_config(seed):
         if kind == "attention":
             kv = r.choice([1, 2, 4])
             h, d = kv * r.choice([1, 2, 4]), r.choice([16, 32, 64, 128, 48])
-            layers.append(attention(h, kv, d, r.choice([d, 32, 64, 128]), rot(r.choice([0, d, d // 2, 8]), r.choice([10000.0, 250000.0, 500.0]), scaling()),
-                                    r.choice([d ** -0.5, 0.125, 0.3]), r.choice([1, 17, 64, 120, 200, 1000]), mlp()))
+            layers.append(attention(h, kv, d, r.choice([d, 32, 64, 128]), rot(r.choice([0, d, d // 2, 8]), r.choice([10000.0, 200000.0, 500.0]), scaling()),
+                                    r.choice([d ** -0.5, 0.125, 0.3]), r.choice([1, 17, 64, 110, 200, 1000]), mlp()))
         elif kind == "parallel":
             kv, kv2 = r.choice([1, 2, 4]), r.choice([1, 2, 3])
             h, d = kv * r.choice([1, 2, 4]), r.choice([16, 32, 64, 128])
-            layers.append(parallel(left(h, kv, d, r.choice([d, 32, 64, 128]), r.choice([d ** -0.5, 0.125]), r.choice([5.0, 20.0, 50.0])),
+            layers.append(parallel(left(h, kv, d, r.choice([d, 32, 64, 128]), r.choice([d ** -0.5, 0.125]), r.choice([5.0, 25.0, 50.0])),
                                    right(kv2 * r.choice([1, 2]), kv2, r.choice([16, 32, 64, 40]), r.choice([16, 32, 64, 24]), r.choice([1, 2, 3, 4, 5])),
                                    r.choice([0.5, 0.8, 1.0]), r.choice([0.5, 1.0, 1.2]), mlp()))
         else:
             d, rd = r.choice([16, 32, 64]), r.choice([8, 16, 32, 64])
             layers.append(latent(r.choice([2, 4, 8, 3]), d, rd, r.choice([16, 32, 64, 128]), r.choice([24, 64, 96, 128]), r.choice([32, 64, 96, 128, 40]),
-                                 r.choice([10000.0, 50000.0]), scaling(), (d + rd) ** -0.5, r.choice([1, 20, 64, 130, 300, 1000]), mlp()))
+                                 r.choice([10000.0, 40000.0]), scaling(), (d + rd) ** -0.5, r.choice([1, 20, 64, 130, 300, 1000]), mlp()))
     return config(r.choice([77, 200, 450, 513]), width, groups, layers, eps=r.choice([1e-5, 1e-6]))
 
 
